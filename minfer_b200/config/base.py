@@ -96,6 +96,11 @@ class ModelPlan:
     # a part of role "model" with ``add(h, ctx, pass_index, embedding_output)``, run before every
     # call of the run order that names a ``pass_start``
     pass_injection: Optional[PartSpec] = None
+    # a part of role "model" that keeps the stream as every entry of the run order leaves it and
+    # hands on a mix of all of them (``begin``, ``slot``, ``mix``: see ``parts.stream.DepthAverage``)
+    after_layer: Optional[PartSpec] = None
+    # tensors a checkpoint may hold although nothing uses them
+    ignorable_tensors: Sequence[str] = ()
 
     def validate(self) -> None:
         if self.vocab_size <= 0 or self.hidden_size <= 0:

@@ -1120,3 +1120,83 @@ extern "C" int mf_add_stream(float* h, const float* other, const void* vec, int 
         return MF_ERR_UNSUPPORTED;
     return MF_LAUNCH_CHECK();
 }
+
+// ------------------------------------------------------------------------------------
+// PolyNorm: y = a rms(z) + b rms(z^2) + c rms(z^3) + e over a row of float32 values, powers
+// element by element, rms(u) = u / sqrt(mean(u^2) + eps); coef = (a, b, c, e) on the device.
+// One block a row: a pass for the three sums of squares, a pass to write.
+// ------------------------------------------------------------------------------------
+template <typename TO>
+__global__ void __launch_bounds__(256)
+poly_norm_kernel(const float* __restrict__ z, const float* __restrict__ coef, TO* __restrict__ out,
+                 int width, float eps) {
+    pdl_launch_dependents();
+    __shared__ float scratch[33];
+    const float a = coef[0], b = coef[1], c = coef[2], e = coef[3];
+    pdl_wait();
+    const float* zr = z + (size_t)blockIdx.x * width;
+    float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = zr[i], v2 = v * v;
+        s2 += v2;
+        s4 = fmaf(v2, v2, s4);
+        s6 = fmaf(v2 * v2, v2, s6);
+    }
+    s2 = block_sum(s2, scratch);
+    s4 = block_sum(s4, scratch);
+    s6 = block_sum(s6, scratch);
+    const float inv_w = 1.0f / (float)width;
+    const float r1 = a / sqrtf(s2 * inv_w + eps), r2 = b / sqrtf(s4 * inv_w + eps),
+                r3 = c / sqrtf(s6 * inv_w + eps);
+    TO* o = out + (size_t)blockIdx.x * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = zr[i], v2 = v * v;
+        o[i] = from_f32<TO>(fmaf(r1, v, fmaf(r2, v2, fmaf(r3, v2 * v, e))));
+    }
+}
+
+extern "C" int mf_poly_norm(const float* z, const float* coef, void* out, int out_dtype, int n_rows,
+                            int width, float eps, cudaStream_t stream) {
+    if (n_rows <= 0 || width <= 0) return 0;
+    if (out_dtype == MF_DTYPE_F32)
+        mf_launch(poly_norm_kernel<float>, dim3(n_rows), dim3(256), 0, stream, z, coef, (float*)out,
+                  width, eps);
+    else if (out_dtype == MF_DTYPE_BF16)
+        mf_launch(poly_norm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, z, coef,
+                  (__nv_bfloat16*)out, width, eps);
+    else return MF_ERR_UNSUPPORTED;
+    return MF_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// Depth-weighted average of the residual streams kept so far:
+//     out[r][:] = sum_{j < n_hist} w[j] hist[j][rows ? rows[r] : r][:] + w[n_hist] last[r][:]
+// `hist` [n_hist][hist_rows][width]; `last` (the newest stream) has the output's rows already.
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+depth_mix_kernel(const float* __restrict__ hist, long long hist_stride, int n_hist,
+                 const int* __restrict__ rows, const float* __restrict__ last,
+                 const float* __restrict__ w, float* __restrict__ out, int n_rows, int width) {
+    pdl_prologue();
+    const long long total = (long long)n_rows * width;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const int r = (int)(i / width), c = (int)(i - (long long)r * width);
+        const long long src = (long long)(rows ? rows[r] : r) * width + c;
+        float acc = 0.f;
+        for (int j = 0; j < n_hist; ++j) acc = fmaf(w[j], hist[(size_t)j * hist_stride + src], acc);
+        out[i] = fmaf(w[n_hist], last[i], acc);
+    }
+}
+
+extern "C" int mf_depth_mix(const float* hist, long long hist_stride, int n_hist, const int* rows,
+                            const float* last, const float* w, float* out, int n_rows, int width,
+                            cudaStream_t stream) {
+    if (n_rows <= 0 || width <= 0) return 0;
+    if (n_hist < 0) return MF_ERR_ARGUMENT;
+    const long long total = (long long)n_rows * width;
+    const long long want = (total + 255) / 256, cap = (long long)mf_sm_count() * 16;
+    mf_launch(depth_mix_kernel, dim3((unsigned)(want < cap ? want : cap)), dim3(256), 0, stream, hist,
+              hist_stride, n_hist, rows, last, w, out, n_rows, width);
+    return MF_LAUNCH_CHECK();
+}

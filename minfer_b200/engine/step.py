@@ -506,6 +506,11 @@ class Engine:
         embedding_output = None
         if model.pass_injection is not None and model.pass_injection.needs_embedding():
             embedding_output = h.clone()
+        # a model that hands on a mix of all streams so far keeps them side by side; every entry
+        # of the run order then works in place on the slot its result belongs in
+        depth, history = model.after_layer, None
+        if depth is not None:
+            history, h = depth.begin(h, ctx)
         bindings = self._bindings(ctx)
         last = len(plan.schedule) - 1
         n_want = 0 if want_rows is None else want_rows.numel()
@@ -538,7 +543,9 @@ class Engine:
                     h = picked
             # the norm that reads h after this block's feed-forward: the next block's first, if
             # it can take its input prepared, or the model's last (the head applies the scale)
-            if i < last:
+            if depth is not None:
+                ctx.extras["next_norm"] = None       # the mix of the streams comes before any norm
+            elif i < last:
                 nxt = plan.schedule[i + 1]
                 # (a pass that starts there changes the stream before that norm reads it)
                 ctx.extras["next_norm"] = (model.blocks[nxt.layer].entry_norm()
@@ -547,6 +554,11 @@ class Engine:
                 ctx.extras["next_norm"] = (model.final_norm if model.head.takes_row_scale()
                                            and model.final_norm.foldable() is not None else None)
             block.feed(h, ctx)
+            if depth is not None:
+                settle_pending(ctx, h)
+                ctx.extras.pop("prepared", None)
+                picked_rows = want_rows if (i == last and not all_rows) else None
+                h = depth.mix(history, i, h, picked_rows)
             if self.layer_tap is not None and (i < last or all_rows):
                 settle_pending(ctx, h)
                 self.layer_tap(i, h)

@@ -114,6 +114,9 @@ def _sig_ops(lib: ctypes.CDLL) -> None:
     lib.mf_xielu.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_longlong, c_void_p]
     lib.mf_tanh_cap.argtypes = [c_void_p, c_longlong, c_float, c_void_p]
     lib.mf_add_stream.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    lib.mf_poly_norm.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
+    lib.mf_depth_mix.argtypes = [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_int, c_int, c_void_p]
 
 
 def _sig_gemm_simt(lib: ctypes.CDLL) -> None:
@@ -208,7 +211,35 @@ def _sig_mixer_prep(lib: ctypes.CDLL) -> None:
     lib.mf_head_linear.argtypes = [c_void_p, c_int, c_void_p]
 
 
-_SIGNATURES = {"attention_prefill_tc": _sig_attention_prefill_tc, "recurrent": _sig_recurrent,
+def _sig_delta_rule(lib: ctypes.CDLL) -> None:
+    lib.mf_delta_scan.argtypes = [c_void_p, c_int, c_void_p]
+    lib.mf_head_norm_gate.argtypes = [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p,
+                                      c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]
+
+
+def _sig_attention_talk(lib: ctypes.CDLL) -> None:
+    lib.mf_talk_attention.argtypes = [c_void_p, c_int, c_int, c_void_p]
+    lib.mf_talk_attention_scratch.argtypes = [c_int, c_int, c_int, c_int]
+    lib.mf_talk_attention_scratch.restype = c_longlong
+    lib.mf_value_mix.argtypes = [c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_void_p,
+                                 c_int, c_int, c_void_p]
+
+
+def _sig_moe(lib: ctypes.CDLL) -> None:
+    lib.mf_moe_route.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    lib.mf_moe_experts.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_longlong,
+                                   c_void_p, c_int, c_void_p,
+                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+    lib.mf_moe_counts.argtypes = [c_void_p, c_void_p, c_int, c_void_p]
+    lib.mf_moe_place.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                 c_void_p]
+    lib.mf_moe_gather.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    lib.mf_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                   c_void_p]
+
+
+_SIGNATURES = {"delta_rule": _sig_delta_rule, "attention_talk": _sig_attention_talk, "moe": _sig_moe,
+               "attention_prefill_tc": _sig_attention_prefill_tc, "recurrent": _sig_recurrent,
                "mixer_prep": _sig_mixer_prep,
                "attention_sink": _sig_attention_sink,
                "attention_prefill": _sig_attention_prefill, "gemm_tc": _sig_gemm_tc, "ops": _sig_ops, "gemm_simt": _sig_gemm_simt, "attention": _sig_attention,
@@ -929,6 +960,247 @@ def head_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, *, x_head: in
     a.tail, a.x_tail_off = int(tail), int(x_tail_off)
     _check(_lib("mixer_prep").mf_head_linear(ctypes.addressof(a), dtype_code(x.dtype), _stream()),
            "head_linear")
+
+
+# ---------------------------------------------------------------------------------------
+# row-wise ops of the residual stream and the feed-forward (csrc/ops.cu)
+# ---------------------------------------------------------------------------------------
+def poly_norm(z: torch.Tensor, coef: torch.Tensor, out: torch.Tensor, eps: float) -> None:
+    """out = a N(z) + b N(z^2) + c N(z^3) + e per row of ``z`` (float32), powers element by
+    element, N(u) = u / sqrt(mean(u^2) + eps); ``coef`` = (a, b, c, e), float32 on the device."""
+    if z.dim() != 2 or out.shape != z.shape or coef.numel() != 4:
+        raise KernelError("poly_norm: shapes do not fit")
+    _check(_lib("ops").mf_poly_norm(_f32(z, "z"), _f32(coef, "coef"), _ptr(out, "out"),
+                                    dtype_code(out.dtype), z.shape[0], z.shape[1], float(eps),
+                                    _stream()), "poly_norm")
+
+
+def depth_mix(history: torch.Tensor, n_hist: int, rows: Optional[torch.Tensor], last: torch.Tensor,
+              weights: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = sum_{j < n_hist} weights[j] history[j][rows[r] or r] + weights[n_hist] last[r]:
+    ``history`` float32 [slots >= n_hist, tokens, width], ``last`` and ``out`` [rows, width]
+    (``out`` may be ``last``: every element is read before it is written, by its own thread)."""
+    if (history.dim() != 3 or last.dim() != 2 or out.shape != last.shape
+            or history.shape[2] != last.shape[1] or n_hist > history.shape[0]
+            or weights.numel() != n_hist + 1):
+        raise KernelError("depth_mix: shapes do not fit")
+    if rows is None and history.shape[1] != last.shape[0]:
+        raise KernelError("depth_mix: without a row index the streams must have the same rows")
+    if rows is not None and rows.numel() != last.shape[0]:
+        raise KernelError("depth_mix: one row index per output row")
+    _check(_lib("ops").mf_depth_mix(_f32(history, "history"), history.stride(0), int(n_hist),
+                                    _i32(rows, "rows"), _f32(last, "last"), _f32(weights, "weights"),
+                                    _f32(out, "out"), last.shape[0], last.shape[1], _stream()),
+           "depth_mix")
+
+
+# ---------------------------------------------------------------------------------------
+# the gated delta rule (csrc/delta_rule.cu)
+# ---------------------------------------------------------------------------------------
+class _DeltaArgs(ctypes.Structure):
+    _fields_ = [("u", c_void_p), ("u_width", c_longlong), ("q_off", c_int), ("k_off", c_int),
+                ("v_off", c_int), ("beta", c_void_p), ("beta_width", c_longlong),
+                ("beta_off", c_int), ("decay", c_void_p), ("decay_width", c_longlong),
+                ("decay_off", c_int), ("dt_bias", c_void_p), ("a_log", c_void_p),
+                ("state", c_void_p), ("cu_seqlens", c_void_p), ("slots", c_void_p),
+                ("out", c_void_p)] + [(n, c_int) for n in ("n_rows", "heads", "kv_heads", "D", "Dv",
+                                                            "per_channel")]
+
+
+def delta_scan(u: torch.Tensor, q_off: int, k_off: int, v_off: int, beta: torch.Tensor,
+               beta_off: int, decay: torch.Tensor, decay_off: int, dt_bias: torch.Tensor,
+               a_log: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor,
+               slots: torch.Tensor, out: torch.Tensor, n_rows: int, max_row_tokens: int, heads: int,
+               kv_heads: int, key_dim: int, value_dim: int, per_channel: bool) -> None:
+    """The gated delta rule per (row, head), tokens one after another, on float32 rows: q, k, v at
+    the columns ``q_off``, ``k_off``, ``v_off`` of ``u`` (after convolution and silu); raw beta at
+    column ``beta_off + h`` of ``beta``; the raw decay input at ``decay_off + h`` of ``decay`` (or
+    ``decay_off + h * key_dim + d`` with ``per_channel``).  q and k become unit vectors per head,
+    q times key_dim^(-1/2); g = exp(-exp(a_log[h]) softplus(raw + dt_bias)); S <- g S;
+    u = sigmoid(beta) (v - S^T k); S <- S + k u^T; out = S^T q.  ``state`` float32
+    [slots, heads, value_dim, key_dim] goes on from what the row's slot holds."""
+    n = u.shape[0]
+    n_decay = heads * key_dim if per_channel else heads
+    if (out.shape != (n, heads * value_dim) or state.shape[1:] != (heads, value_dim, key_dim)
+            or beta.shape[0] != n or decay.shape[0] != n or dt_bias.numel() != n_decay
+            or a_log.numel() != heads or beta_off + heads > beta.shape[1]
+            or decay_off + n_decay > decay.shape[1]
+            or max(q_off, k_off) + kv_heads * key_dim > u.shape[1]
+            or v_off + heads * value_dim > u.shape[1]):
+        raise KernelError("delta_scan: shapes do not fit")
+    a = _DeltaArgs()
+    a.u, a.u_width, a.q_off, a.k_off, a.v_off = _f32(u, "u"), u.shape[1], int(q_off), int(k_off), int(v_off)
+    a.beta, a.beta_width, a.beta_off = _f32(beta, "beta"), beta.shape[1], int(beta_off)
+    a.decay, a.decay_width, a.decay_off = _f32(decay, "decay"), decay.shape[1], int(decay_off)
+    a.dt_bias, a.a_log, a.state = _f32(dt_bias, "dt_bias"), _f32(a_log, "a_log"), _f32(state, "state")
+    a.cu_seqlens, a.slots = _i32(cu_seqlens, "cu_seqlens"), _i32(slots, "slots")
+    a.out = _f32(out, "out")
+    a.n_rows, a.heads, a.kv_heads, a.D, a.Dv = int(n_rows), heads, kv_heads, key_dim, value_dim
+    a.per_channel = 1 if per_channel else 0
+    _check(_lib("delta_rule").mf_delta_scan(ctypes.addressof(a), int(max_row_tokens), _stream()),
+           "delta_scan")
+
+
+HEAD_GATES = {"silu": 0, "sigmoid": 1}
+
+
+def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, gate_off: int, weight: torch.Tensor,
+                   out: torch.Tensor, heads: int, value_dim: int, eps: float, gate_act: str) -> None:
+    """out[t][h] = o[t][h] / sqrt(mean(o[t][h]^2) + eps) * weight * act(gate[t][gate_off + h * Dv ..]),
+    ``weight`` [value_dim] shared by the heads, act silu or sigmoid; o and gate float32 rows."""
+    n = o.shape[0]
+    if (o.shape != (n, heads * value_dim) or out.shape != o.shape or weight.numel() != value_dim
+            or gate.shape[0] != n or gate_off + heads * value_dim > gate.shape[1]):
+        raise KernelError("head_norm_gate: shapes do not fit")
+    _check(_lib("delta_rule").mf_head_norm_gate(
+        _f32(o, "o"), _f32(gate, "gate"), gate.shape[1], int(gate_off), _f32(weight, "weight"),
+        _ptr(out, "out"), dtype_code(out.dtype), n, heads, value_dim, float(eps),
+        HEAD_GATES[gate_act], _stream()), "head_norm_gate")
+
+
+# ---------------------------------------------------------------------------------------
+# attention whose heads' scores are mixed before the softmax (csrc/attention_talk.cu)
+# ---------------------------------------------------------------------------------------
+class _TalkArgs(ctypes.Structure):
+    _fields_ = ([(n, c_void_p) for n in ("q", "k", "v", "row_seq", "row_pos", "cu_seqlens",
+                                         "page_table")] +
+                [("table_stride", c_int), ("ring", c_int), ("talk", c_void_p), ("gate", c_void_p),
+                 ("gate_width", c_longlong), ("gate_off", c_int), ("out", c_void_p),
+                 ("scratch", c_void_p)] +
+                [(n, c_int) for n in ("rows", "heads", "n_kv", "hd", "vd", "window", "splits")] +
+                [("scale", c_float)])
+
+
+def talk_attention_splits(rows: int, reach_keys: int) -> int:
+    """Stretches a query's keys are cut into: enough blocks to fill the GPU when the queries are
+    few and their keys many (at least 128 keys a stretch)."""
+    if rows <= 0:
+        return 1
+    want = max(1, (2 * 148) // rows)
+    return max(1, min(want, reach_keys // 128, 32))
+
+
+def talk_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, row_seq: torch.Tensor,
+                   row_pos: torch.Tensor, cu_seqlens: Optional[torch.Tensor],
+                   page_table: Optional[torch.Tensor], table_stride: int, ring: int,
+                   talk: torch.Tensor, gate: Optional[torch.Tensor], gate_off: int,
+                   out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, value_dim: int,
+                   window: int, scale: float, reach_keys: int = 0) -> None:
+    """Softmax attention with s'_h = sum_g talk[h][g] (q_g . k) * scale, causal with an optional
+    window, over the step's packed keys (``page_table`` None: key j of batch row b at token
+    cu_seqlens[b] + j) or over the cache's pages; head h's output times sigmoid(gate[row][gate_off
+    + h]) if ``gate`` (float32 rows) is given.  ``reach_keys``: a bound on the keys a query sees,
+    used to cut long stretches over several blocks."""
+    rows = q.shape[0]
+    paged = page_table is not None
+    if out.shape != (rows, n_heads * value_dim) or talk.shape != (n_heads, n_heads):
+        raise KernelError("talk_attention: shapes do not fit")
+    if k.dtype != q.dtype or v.dtype != q.dtype or out.dtype != q.dtype:
+        raise KernelError("talk_attention: q, k, v and the output must share one dtype")
+    splits = talk_attention_splits(rows, reach_keys) if reach_keys > 0 else 1
+    scratch = None
+    if splits > 1:
+        scratch = torch.empty(rows * splits * n_heads * (value_dim + 2), dtype=torch.float32,
+                              device=q.device)
+    a = _TalkArgs()
+    a.q, a.k, a.v = _ptr(q, "q"), _ptr(k, "k"), _ptr(v, "v")
+    a.row_seq, a.row_pos = _i32(row_seq, "row_seq"), _i32(row_pos, "row_pos")
+    a.cu_seqlens, a.page_table = _i32(cu_seqlens, "cu_seqlens"), _i32(page_table, "page_table")
+    a.table_stride, a.ring = int(table_stride), int(ring)
+    a.talk, a.gate = _f32(talk, "talk"), _f32(gate, "gate")
+    a.gate_width = gate.shape[1] if gate is not None else 0
+    a.gate_off, a.out, a.scratch = int(gate_off), _ptr(out, "out"), _f32(scratch, "scratch")
+    a.rows, a.heads, a.n_kv, a.hd, a.vd = rows, n_heads, n_kv, head_dim, value_dim
+    a.window, a.splits, a.scale = int(window), splits, float(scale)
+    _check(_lib("attention_talk").mf_talk_attention(ctypes.addressof(a), 1 if paged else 0,
+                                                    dtype_code(q.dtype), _stream()),
+           "talk_attention", 2 if splits > 1 else 1)
+
+
+def value_mix(proj: torch.Tensor, v_off: int, first: torch.Tensor, first_off: int,
+              lam: torch.Tensor, width: int) -> None:
+    """proj[:, v_off : v_off + width] <- (1 - lam) that + lam first[:, first_off : ..] on float32
+    rows; ``lam`` one float32 number on the device."""
+    n = proj.shape[0]
+    if first.shape[0] != n or v_off + width > proj.shape[1] or first_off + width > first.shape[1]:
+        raise KernelError("value_mix: shapes do not fit")
+    _check(_lib("attention_talk").mf_value_mix(
+        _f32(proj, "proj"), proj.shape[1], int(v_off), _f32(first, "first"), first.shape[1],
+        int(first_off), _f32(lam, "lam"), n, int(width), _stream()), "value_mix")
+
+
+# ---------------------------------------------------------------------------------------
+# routed experts (csrc/moe.cu)
+# ---------------------------------------------------------------------------------------
+def moe_route(logits: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, top: int) -> None:
+    """Per row of ``logits`` (float32 [tokens, experts]): the ``top`` largest (ties: the lower
+    index) into ``idx`` (int32 [tokens, top]) and the softmax over the chosen into ``wts``."""
+    n, experts = logits.shape
+    if idx.shape != (n, top) or wts.shape != (n, top):
+        raise KernelError("moe_route: shapes do not fit")
+    _check(_lib("moe").mf_moe_route(_f32(logits, "logits"), _i32(idx, "idx"), _f32(wts, "wts"), n,
+                                    experts, int(top), _stream()), "moe_route")
+
+
+def moe_experts(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
+                idx: torch.Tensor, wts: torch.Tensor, hidden: torch.Tensor, h: torch.Tensor) -> None:
+    """h[t] += sum_k wts[t][k] Wd_e (silu(Wg_e x_t) * (Wu_e x_t)), e = idx[t][k].  ``w_gate`` and
+    ``w_up`` [experts, ff, width] are two stacks or strided views of one stack with alternating
+    rows (equal strides, rows contiguous); ``w_down`` [experts, width, ff]; ``hidden``
+    [tokens, top, ff] in the type of ``x`` is scratch; ``h`` float32.  For steps of few tokens (a
+    product per token)."""
+    n, width = x.shape
+    experts, ff, _ = w_gate.shape
+    top = idx.shape[1]
+    if (w_up.shape != w_gate.shape or w_down.shape != (experts, width, ff) or w_gate.shape[2] != width
+            or hidden.shape != (n, top, ff) or hidden.dtype != x.dtype or h.shape != (n, width)
+            or w_up.dtype != w_gate.dtype or w_down.dtype != w_gate.dtype
+            or w_gate.stride() != w_up.stride() or w_gate.stride(2) != 1):
+        raise KernelError("moe_experts: shapes do not fit")
+    if not (w_gate.is_cuda and w_up.is_cuda):
+        raise KernelError("moe_experts: the weights must live on a CUDA device")
+    _check(_lib("moe").mf_moe_experts(
+        _ptr(x, "x"), dtype_code(x.dtype), w_gate.data_ptr(), w_up.data_ptr(), w_gate.stride(1),
+        w_gate.stride(0), _ptr(w_down, "w_down"), dtype_code(w_gate.dtype), _i32(idx, "idx"),
+        _f32(wts, "wts"), _ptr(hidden, "hidden"), _f32(h, "h"), n, width, ff, top, _stream()),
+        "moe_experts", 2)
+
+
+def moe_counts(idx: torch.Tensor, counts: torch.Tensor) -> None:
+    """counts[e] += number of entries of ``idx`` equal to e (int32; zero it first)."""
+    _check(_lib("moe").mf_moe_counts(_i32(idx, "idx"), _i32(counts, "counts"), idx.numel(),
+                                     _stream()), "moe_counts")
+
+
+def moe_place(idx: torch.Tensor, counts: torch.Tensor, offsets: torch.Tensor, order: torch.Tensor,
+              where: torch.Tensor) -> None:
+    """Groups the (token, choice) pairs of ``idx`` by expert: offsets[e] = first row of expert e
+    (int32 [experts + 1]), where[pair] = the pair's row, order[row] = its pair; an expert's pairs
+    keep their order."""
+    n_pairs, experts = idx.numel(), counts.numel()
+    if offsets.numel() != experts + 1 or order.numel() != n_pairs or where.numel() != n_pairs:
+        raise KernelError("moe_place: shapes do not fit")
+    _check(_lib("moe").mf_moe_place(_i32(idx, "idx"), _i32(counts, "counts"), _i32(offsets, "offsets"),
+                                    _i32(order, "order"), _i32(where, "where"), n_pairs, experts,
+                                    _stream()), "moe_place", 2)
+
+
+def moe_gather(x: torch.Tensor, pairs: torch.Tensor, out: torch.Tensor, top: int) -> None:
+    """out[i] = x[pairs[i] // top]: the rows of the tokens behind the (token, choice) pairs."""
+    if out.shape != (pairs.numel(), x.shape[1]) or out.dtype != x.dtype:
+        raise KernelError("moe_gather: shapes do not fit")
+    _check(_lib("moe").mf_moe_gather(_ptr(x, "x"), dtype_code(x.dtype), _i32(pairs, "pairs"),
+                                     _ptr(out, "out"), pairs.numel(), x.shape[1], int(top),
+                                     _stream()), "moe_gather")
+
+
+def moe_combine(y: torch.Tensor, where: torch.Tensor, wts: torch.Tensor, h: torch.Tensor) -> None:
+    """h[t] += sum_k wts[t][k] y[where[t][k]], the choices in order; y float32 rows."""
+    n, top = where.shape
+    if wts.shape != (n, top) or h.shape != (n, y.shape[1]):
+        raise KernelError("moe_combine: shapes do not fit")
+    _check(_lib("moe").mf_moe_combine(_f32(y, "y"), _i32(where, "where"), _f32(wts, "wts"),
+                                      _f32(h, "h"), n, y.shape[1], top, _stream()), "moe_combine")
 
 
 # ---------------------------------------------------------------------------------------

@@ -39,6 +39,9 @@ LIBRARIES = {
     "attention_sink": ("attention_sink.cu", []),
     "recurrent": ("recurrent.cu", []),
     "mixer_prep": ("mixer_prep.cu", []),
+    "delta_rule": ("delta_rule.cu", []),
+    "attention_talk": ("attention_talk.cu", []),
+    "moe": ("moe.cu", []),
 }
 
 

@@ -49,6 +49,8 @@ class Model:
         self.on_logits = build_part("model", plan.on_logits) if plan.on_logits is not None else None
         self.pass_injection = (build_part("model", plan.pass_injection)
                                if plan.pass_injection is not None else None)
+        self.after_layer = (build_part("model", plan.after_layer)
+                            if plan.after_layer is not None else None)
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[Linear] = None
         self.device: Optional[torch.device] = None
@@ -75,14 +77,15 @@ class Model:
 
     def model_parts(self) -> List[Any]:
         """The plan's parts around the blocks that this model has."""
-        return [part for part in (self.after_embedding, self.on_logits, self.pass_injection)
-                if part is not None]
+        return [part for part in (self.after_embedding, self.on_logits, self.pass_injection,
+                                  self.after_layer) if part is not None]
 
     def ignorable_tensors(self) -> List[str]:
         """Names a checkpoint may hold without being used: a separate head beside tied
         embeddings (the reference uses the embedding table whenever there is no output
         matrix: src/models/qwen2/loader.rs:256-263)."""
-        return ["lm_head.weight"] if self.plan.head_name is None else []
+        tied = ["lm_head.weight"] if self.plan.head_name is None else []
+        return tied + list(self.plan.ignorable_tensors)
 
     # ---- taking weights in ----------------------------------------------------------------
     def bind(self, weights: Dict[str, torch.Tensor], device: torch.device | str) -> "Model":
@@ -105,6 +108,14 @@ class Model:
         with open(path, "r", encoding="utf-8") as f:
             raw = json.load(f)
         config = read_config(raw, path)
+        if hasattr(config, "with_tensor_shapes"):
+            # a design some of whose sizes only the tensors' shapes give
+            from .weights.safetensors_io import Checkpoint
+            ck = Checkpoint(folder)
+            try:
+                config = config.with_tensor_shapes({n: tuple(ck.entry(n).shape) for n in ck.names()})
+            finally:
+                ck.close()
         model = cls(config.plan(), dtype, config)
         specs = model.tensor_specs()
         weights = load_weights(folder, specs, model.dtype, device, model.ignorable_tensors())

@@ -4,17 +4,20 @@ from .attention import Attention
 from .base import (Block, CacheRequest, CacheView, CallBinding, FeedForward, Mixer, Norm, Part,
                    PositionEncoding, StateRequest, StepContext)
 from .block import PreNormBlock
+from .delta_rule import GatedDeltaRule
 from .latent_attention import LatentAttention
 from .linear import Linear
 from .mamba2 import Mamba2
 from .mlp import DenseMlp, GatedMlp
+from .moe import RoutedExperts
 from .norm import RmsNorm
 from .positions import LearnedPositions
 from .qknorm_attention import QkNormAttention
 from .rotary import NoPosition, Rotary
 from .shift import TokenShift
 from .sink_attention import SinkAttention
-from .stream import EmbeddingNorm, LogitSoftcap, PassInjection
+from .talking_attention import TalkingAttention
+from .stream import DepthAverage, EmbeddingNorm, LogitSoftcap, PassInjection
 
 register_part("norm", "rms_norm", RmsNorm, replace=True)
 register_part("position", "rotary", Rotary, replace=True)
@@ -24,11 +27,15 @@ register_part("mixer", "sink_attention", SinkAttention, replace=True)
 register_part("mixer", "qk_norm_attention", QkNormAttention, replace=True)
 register_part("mixer", "latent_attention", LatentAttention, replace=True)
 register_part("mixer", "mamba2", Mamba2, replace=True)
+register_part("mixer", "gated_delta_rule", GatedDeltaRule, replace=True)
+register_part("mixer", "talking_attention", TalkingAttention, replace=True)
 register_part("feed_forward", "gated_mlp", GatedMlp, replace=True)
 register_part("feed_forward", "dense_mlp", DenseMlp, replace=True)
+register_part("feed_forward", "routed_experts", RoutedExperts, replace=True)
 register_part("model", "learned_positions", LearnedPositions, replace=True)
 register_part("model", "embedding_norm", EmbeddingNorm, replace=True)
 register_part("model", "logit_softcap", LogitSoftcap, replace=True)
 register_part("model", "pass_injection", PassInjection, replace=True)
+register_part("model", "depth_average", DepthAverage, replace=True)
 register_part("block", "pre_norm", lambda layer, **options: PreNormBlock(layer, **options),
               replace=True)

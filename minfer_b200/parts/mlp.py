@@ -123,24 +123,30 @@ class DenseMlp(FeedForward):
                  z > 0: softplus(a0) z^2 + z/2;  z <= 0: (1/2 + softplus(a1)) (exp(z) - 1 - z) + z/2,
                  evaluated in float32 on the product's float32 sums.
 
+    ``"poly_norm"``  with four learned numbers (a, b, c, e): a N(z) + b N(z^2) + c N(z^3) + e,
+                 powers element by element, N(u) = u / sqrt(mean(u^2) + eps) over a token's
+                 feed-forward values (``norm_eps``), in float32 on the product's float32 sums.
+
     Tensor names are parameters (``up_name``, ``down_name``, ``act_name``, each behind the
     layer's prefix)."""
 
     capturable = True      # launches kernels only; safe inside a CUDA graph capture
-    ACTIVATIONS = ("xielu",)
+    ACTIVATIONS = ("xielu", "poly_norm")
+    ACT_NUMBERS = {"xielu": 2, "poly_norm": 4}
 
     def libraries(self, dtype: torch.dtype) -> List[str]:
         return ["ops", "gemm_tc"] if dtype == torch.bfloat16 else ["ops", "gemm_simt"]
 
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "xielu",
                  up_name: str = "mlp.up", down_name: str = "mlp.down", act_name: str = "mlp.act",
-                 init_std: float = 0.02):
+                 init_std: float = 0.02, norm_eps: float = 1e-6):
         if activation not in self.ACTIVATIONS:
             raise ValueError(f"the dense feed-forward has the activations {self.ACTIVATIONS}, got "
                              f"{activation!r}")
         self.hidden_size = int(hidden_size)
         self.intermediate_size = int(intermediate_size)
         self.activation = activation
+        self.norm_eps = float(norm_eps)
         self.up_name, self.down_name, self.act_name = up_name, down_name, act_name
         self.init_std = float(init_std)
         self.up: Optional[Linear] = None
@@ -153,13 +159,16 @@ class DenseMlp(FeedForward):
                            MATRIX, init),
                 TensorSpec(f"{prefix}{self.down_name}", (self.hidden_size, self.intermediate_size),
                            MATRIX, init),
-                TensorSpec(f"{prefix}{self.act_name}", (2,), VECTOR, Init(0.0, 0.5))]
+                TensorSpec(f"{prefix}{self.act_name}", (self.ACT_NUMBERS[self.activation],), VECTOR,
+                           Init(0.0, 0.5))]
 
     def load(self, prefix: str, weights: Dict[str, torch.Tensor]) -> None:
         self.up = Linear(weights[f"{prefix}{self.up_name}"])
         self.down = Linear(weights[f"{prefix}{self.down_name}"])
         self.act_params = weights[f"{prefix}{self.act_name}"]
         self.accepts_row_scale = self.up.takes_row_scale()
+        if self.activation != "xielu":
+            return
         # the activation's two coefficients, once, for the product whose epilogue applies it
         a = self.act_params.detach().to("cpu", torch.float64)
         sp = torch.log1p(torch.exp(-a.abs())) + torch.clamp(a, min=0)
@@ -172,7 +181,12 @@ class DenseMlp(FeedForward):
     def forward_add(self, x: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
         from ..kernels import gemm
         act = torch.empty((x.shape[0], self.intermediate_size), dtype=ctx.act_dtype, device=x.device)
-        if (x.shape[0] > 0 and self.up.takes_row_scale() and x.dtype == torch.bfloat16
+        if self.activation == "poly_norm":
+            # a row's three sums come before any of its outputs: the activation is a kernel of
+            # its own on the product's float32 rows
+            z = self.up.forward(x, torch.float32, row_scale=ctx.input_scale)
+            K.poly_norm(z, self.act_params, act, self.norm_eps)
+        elif (x.shape[0] > 0 and self.up.takes_row_scale() and x.dtype == torch.bfloat16
                 and K.gemm_tc_supported(x, self.up.weight) and FUSE_ACTIVATION):
             # the activation rides on the up projection's epilogue
             K.gemm_tc_xielu(x, self.up.weight, act, self._act_p, self._act_n,
