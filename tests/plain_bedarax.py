@@ -166,8 +166,20 @@ def route(y: torch.Tensor, w_router: torch.Tensor, b_router: torch.Tensor, top: 
     return idx, torch.softmax(val, dim=-1)
 
 
-def routed_ff(y, w, p, spec):
+def route_margin(y: torch.Tensor, w_router: torch.Tensor, b_router: torch.Tensor, top: int):
+    """Per token, by how much the last chosen logit leads the first one left out (inf when every
+    expert is chosen): a rounding error of that size in the logits changes the choice."""
+    z = y @ w_router.T + b_router
+    if top >= z.shape[-1]:
+        return torch.full((z.shape[0],), float("inf"), dtype=z.dtype)
+    ranked, _ = torch.sort(z, dim=-1, descending=True)
+    return ranked[:, top - 1] - ranked[:, top]
+
+
+def routed_ff(y, w, p, spec, margins: Optional[List[torch.Tensor]] = None):
     idx, wts = route(y, w[p + "router"], w[p + "router.b"], spec["router"]["top"])
+    if margins is not None:
+        margins.append(route_margin(y, w[p + "router"], w[p + "router.b"], spec["router"]["top"]))
     out = torch.zeros((y.shape[0], w[p + "e0.down"].shape[0]), dtype=y.dtype)
     for t in range(y.shape[0]):
         for j in range(idx.shape[1]):
@@ -179,9 +191,10 @@ def routed_ff(y, w, p, spec):
 
 # ---- the model -----------------------------------------------------------------------------------
 def forward(config: Mapping, w: Mapping[str, torch.Tensor], ids: List[int],
-            taps: Optional[List[torch.Tensor]] = None) -> torch.Tensor:
+            taps: Optional[List[torch.Tensor]] = None,
+            margins: Optional[List[torch.Tensor]] = None) -> torch.Tensor:
     """Logits [n, vocab] of one sequence.  ``taps`` collects the stream after every layer (after
-    the depth average)."""
+    the depth average), ``margins`` every router's margin per token (``route_margin``)."""
     eps = float(config["norm"]["eps"])
     x = rms_norm(w["embed"][torch.tensor(ids, dtype=torch.long)], w["embed.norm"], eps)
     history = [x]
@@ -201,13 +214,25 @@ def forward(config: Mapping, w: Mapping[str, torch.Tensor], ids: List[int],
         if mlp is not None:
             u2 = rms_norm(y, w[p + "norm2"], eps)
             y = y + (dense_ff(u2, w, p + "mlp.", eps) if mlp["kind"] == "dense"
-                     else routed_ff(u2, w, p + "mlp.", mlp))
+                     else routed_ff(u2, w, p + "mlp.", mlp, margins))
         history.append(y)
         c = w[p + "dwa"]
         x = sum(c[j] * history[j] for j in range(i + 2))
         if taps is not None:
             taps.append(x.clone())
     return rms_norm(x, w["final.norm"], eps) @ w["head"].T
+
+
+def forward_sure(config: Mapping, w: Mapping[str, torch.Tensor], ids: List[int],
+                 least_margin: float) -> torch.Tensor:
+    """``forward`` with NaN in the rows of every token for which some router's choice hangs on
+    less than ``least_margin``: an implementation that rounds its activations may choose otherwise
+    there, rightly, so a comparison leaves those rows out."""
+    margins: List[torch.Tensor] = []
+    logits = forward(config, w, ids, None, margins).clone()
+    for m in margins:
+        logits[m < least_margin] = float("nan")
+    return logits
 
 
 def generate_greedy(config: Mapping, w: Mapping[str, torch.Tensor], prompt: List[int],
@@ -218,3 +243,17 @@ def generate_greedy(config: Mapping, w: Mapping[str, torch.Tensor], prompt: List
         out.append(tok)
         ids.append(tok)
     return out
+
+
+def load_folder(folder: str, dtype: torch.dtype = torch.float64):
+    """(config.json as a dict, every tensor of model.safetensors in ``dtype``)."""
+    import json
+    import os
+    from safetensors import safe_open
+    with open(os.path.join(folder, "config.json")) as f:
+        cfg = json.load(f)
+    weights = {}
+    with safe_open(os.path.join(folder, "model.safetensors"), framework="pt") as f:
+        for name in f.keys():
+            weights[name] = f.get_tensor(name).to(dtype)
+    return cfg, weights
