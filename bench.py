@@ -741,6 +741,283 @@ def workload_budanex(args) -> int:
     return 0
 
 
+# --workload bedarax: the Bedarax design beside the Qwen2 decoder at equal width and layers
+# ------------------------------------------------------------------------------------------
+# (name, width, attention heads, kv heads, head size, feed-forward width, recurrent heads, their
+#  query/key heads, window, experts, experts a token): six layers [delta rule + routed experts,
+# talking attention + dense PolyNorm feed-forward, channel-wise delta rule + routed experts] x 2;
+# an expert is half as wide as the dense feed-forward, so two of them make its width
+BEDARAX_SIZES = [("w2048", 2048, 16, 4, 128, 5632, 16, 8, 1024, 8, 2),
+                 ("w4096", 4096, 32, 8, 128, 11264, 32, 16, 2048, 8, 2)]
+BEDARAX_LAYERS = 6
+
+
+def bedarax_config(width, heads, kv, dim, ff, rec_heads, rec_kv, window, experts, top, vocab):
+    moe = {"kind": "moe", "expert": {"ff": ff // 2}, "router": {"experts": experts, "top": top}}
+    delta = {"type": "delta", "mlp": moe,
+             "mixer": {"heads": rec_heads, "kv_heads": rec_kv, "dim": 128, "vdim": 128, "conv": 4}}
+    channel = {"type": "channel_delta", "mlp": moe,
+               "mixer": {"heads": rec_heads, "kv_heads": rec_kv, "dim": 128, "vdim": 128, "conv": 4,
+                         "a_rank": 64, "g_rank": 64}}
+    attention = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
+                 "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim,
+                           "scale": dim ** -0.5, "mask": {"size": window}, "v_mix": True}}
+    return {"architecture": "Bedarax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "layers": [delta, attention, channel, delta, attention, channel]}
+
+
+def bedarax_prefill_flops(cfg, tokens):
+    """Matrix-product flops of one whole prompt (head on the last row only; the experts a token
+    uses, not all), the attention of the visible keys with the mix of the heads' scores, and the
+    recurrence (decay, two products with the state and the rank-one update per token)."""
+    w, n = cfg["width"], tokens
+    flops = 0.0
+    for layer in cfg["layers"]:
+        m = layer["mixer"]
+        h, g, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        pairs = 0.0
+        if layer["type"] == "attention":
+            per_token = 2 * w * (h * d + g * d + g * dv + h) + 2 * w * h * dv
+            c = m["mask"]["size"]
+            seen = n * (n + 1) / 2 if n <= c else c * (c + 1) / 2 + (n - c) * c
+            pairs = (h * 2 * (d + dv) + 2 * h * h) * seen
+        else:
+            a_in = m.get("a_rank", 0) or h
+            g_in = m.get("g_rank", 0) or h * dv
+            per_token = 2 * w * (2 * g * d + h * dv + h + a_in + g_in) + 2 * w * h * dv
+            if layer["type"] == "channel_delta":
+                per_token += 2 * m["a_rank"] * h * d + 2 * m["g_rank"] * h * dv
+            per_token += 8 * h * d * dv
+        mlp = layer["mlp"]
+        if mlp is not None and mlp["kind"] == "dense":
+            per_token += 4 * w * mlp["ff"]
+        elif mlp is not None:
+            per_token += mlp["router"]["top"] * 6 * w * mlp["expert"]["ff"] + 2 * w * mlp["router"]["experts"]
+        flops += per_token * n + pairs
+    return flops + 2 * w * cfg["vocab"]
+
+
+def bedarax_decode_bytes(model, cfg, batch, context_tokens):
+    """``decode_bytes`` with the experts a step can touch at most (batch x top of each layer's)
+    in place of all of them."""
+    total = decode_bytes(model, batch, context_tokens)
+    for layer in cfg["layers"]:
+        mlp = layer["mlp"]
+        if mlp is not None and mlp["kind"] == "moe":
+            experts, top = mlp["router"]["experts"], mlp["router"]["top"]
+            idle = max(0, experts - batch * top)
+            total -= idle * 3 * cfg["width"] * mlp["expert"]["ff"] * 2
+    return total
+
+
+def bedarax_kernels(torch, K, pk, width, heads, kv, dim, ff, rec_heads, rec_kv, window, experts, top,
+                    tokens=2048, batch=8):
+    """The design's own kernels alone (median of 20, L2 flushed before each): device time and the
+    fraction of the copy bandwidth (or of the product peak) their algorithmic bytes (flops) reach,
+    each beside the like kernel of another design at equal sizes."""
+    dev = "cuda:0"
+    bw = pk["hbm_gbs"] * 1e9
+    peak = pk["bf16_tflops"] * 1e12
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    bf = torch.bfloat16
+    out = {}
+
+    def timed(name, fn, nbytes):
+        ms = _median_ms(torch, fn, 20, flush)
+        out[name] = {"us": round(ms * 1e3, 1), "frac_of_copy": round(nbytes / (ms * 1e-3) / bw, 4)}
+
+    D = Dv = 128
+    for label, n, rows in (("prompt", tokens, 1), ("decode", batch, batch)):
+        per = n // rows
+        qk, vw = rec_kv * D, rec_heads * Dv
+        ch = 2 * qk + vw
+        token_row = torch.arange(rows, dtype=torch.int32, device=dev).repeat_interleave(per)
+        cu = torch.arange(rows + 1, dtype=torch.int32, device=dev) * per
+        slots = torch.arange(rows, dtype=torch.int32, device=dev)
+        for kind, n_decay in (("head", rec_heads), ("channel", rec_heads * D)):
+            proj = torch.randn(n, ch + rec_heads, device=dev)
+            decay = torch.randn(n, n_decay, device=dev)
+            gate = torch.randn(n, vw, device=dev)
+            u = torch.randn(n, ch, device=dev) * 0.5
+            state = torch.zeros(rows + 1, rec_heads, Dv, D, device=dev)
+            dt_bias = torch.full((n_decay,), -1.0, device=dev)
+            a_log = torch.zeros(rec_heads, device=dev)
+            o = torch.empty(n, vw, device=dev)
+            timed(f"delta_scan_{kind}_{label}",
+                  lambda: K.delta_scan(u, 0, qk, 2 * qk, proj, ch, decay, 0, dt_bias, a_log, state, cu,
+                                       slots, o, rows, per, rec_heads, rec_kv, D, Dv, kind == "channel"),
+                  n * (ch + rec_heads + n_decay + vw) * 4 + rows * rec_heads * D * Dv * 8)
+            out[f"delta_scan_{kind}_{label}"]["frac_of_fp32_fma"] = round(
+                n * rec_heads * D * Dv * 4 / (out[f"delta_scan_{kind}_{label}"]["us"] * 1e-6)
+                / (148 * 128 * 1.9e9), 4)
+        g16 = torch.empty(n, vw, dtype=bf, device=dev)
+        nw = torch.ones(Dv, device=dev)
+        timed(f"head_norm_gate_{label}", lambda: K.head_norm_gate(o, gate, 0, nw, g16, rec_heads, Dv,
+                                                                   1e-5, "silu"),
+              n * vw * (4 + 4 + 2))
+        conv_w = torch.randn(ch, 4, device=dev) * 0.3
+        conv_state = torch.zeros(rows + 1, ch, 3, device=dev)
+        praw = torch.randn(n, ch, device=dev)
+        timed(f"conv_silu_{label}", lambda: K.conv_silu(praw, 0, ch, conv_w, None, conv_state, token_row,
+                                                         cu, slots, u, rows, single=(per == 1)),
+              n * ch * 8 + (rows * ch * 3 * 8 if per == 1 else 0))
+        # the state-space scan of the Budanex design at an equal state (heads x 64 x 128 floats)
+        sh, P_, N = rec_heads * 2, 64, 128
+        inner, sch = sh * P_, sh * P_ + 2 * N
+        sproj = torch.randn(n, 2 * inner + 2 * N + sh, device=dev)
+        su = torch.randn(n, sch, device=dev) * 0.5
+        sstate = torch.zeros(rows + 1, sh, P_, N, device=dev)
+        sy = torch.empty(n, inner, device=dev)
+        zero = torch.zeros(sh, device=dev)
+        timed(f"budanex_ssm_scan_{label}", lambda: K.ssm_scan(su, sproj, inner + sch, zero, zero, zero,
+                                                               sstate, cu, slots, sy, rows, sh, P_, N, 1),
+              n * (sch + inner + sh) * 4 + rows * sh * P_ * N * 8)
+        out[f"budanex_ssm_scan_{label}"]["frac_of_fp32_fma"] = round(
+            n * sh * P_ * N * 3 / (out[f"budanex_ssm_scan_{label}"]["us"] * 1e-6) / (148 * 128 * 1.9e9), 4)
+        # the stream's row-wise kernels
+        z = torch.randn(n, ff, device=dev)
+        zo = torch.empty(n, ff, dtype=bf, device=dev)
+        coef = torch.tensor([0.5, 0.3, 0.2, 0.1], device=dev)
+        timed(f"poly_norm_{label}", lambda: K.poly_norm(z, coef, zo, 1e-5), n * ff * 6)
+        hist = torch.randn(BEDARAX_LAYERS + 1, n, width, device=dev)
+        last = torch.randn(n, width, device=dev)
+        wts = torch.randn(BEDARAX_LAYERS + 1, device=dev)
+        timed(f"depth_mix_{label}", lambda: K.depth_mix(hist, BEDARAX_LAYERS, None, last, wts, last),
+              (BEDARAX_LAYERS + 2) * n * width * 4)
+        nv = kv * dim
+        aproj = torch.randn(n, heads * dim + 2 * nv + heads, device=dev)
+        first = torch.randn(n, heads * dim + 2 * nv + heads, device=dev)
+        lam = torch.tensor(0.4, device=dev)
+        timed(f"value_mix_{label}", lambda: K.value_mix(aproj, heads * dim + nv, first, heads * dim + nv,
+                                                        lam, nv), n * nv * 12)
+    # routed experts, the per-token kernels of a decode step: every chosen expert's matrices once
+    x8 = torch.randn(batch, width, device=dev).to(bf)
+    eff = ff // 2
+    wg = (torch.randn(experts, 2 * eff, width, device=dev) * 0.02).to(bf)
+    pairs = wg.view(experts, eff, 2, width)
+    wd = (torch.randn(experts, width, eff, device=dev) * 0.02).to(bf)
+    logits = torch.randn(batch, experts, device=dev)
+    idx = torch.empty(batch, top, dtype=torch.int32, device=dev)
+    rw = torch.empty(batch, top, device=dev)
+    hidden = torch.empty(batch, top, eff, dtype=bf, device=dev)
+    res = torch.zeros(batch, width, device=dev)
+    timed("moe_route_decode", lambda: K.moe_route(logits, idx, rw, top), batch * experts * 4)
+    K.moe_route(logits, idx, rw, top)
+    timed("moe_experts_decode", lambda: K.moe_experts(x8, pairs[:, :, 0], pairs[:, :, 1], wd, idx, rw,
+                                                      hidden, res),
+          batch * top * 3 * eff * width * 2)
+    # attention: the talking kernel beside the plain-score kernels at equal sizes
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    cu1 = torch.tensor([0, tokens], dtype=torch.int32, device=dev)
+    qq = (torch.randn(tokens, heads, dim, device=dev) * 0.5).to(bf)
+    kk = (torch.randn(tokens, kv, dim, device=dev) * 0.5).to(bf)
+    vv = torch.randn(tokens, kv, dim, device=dev).to(bf)
+    oo = torch.empty(tokens, heads * dim, dtype=bf, device=dev)
+    talk = torch.eye(heads, device=dev) + torch.randn(heads, heads, device=dev) * 0.1
+    gate = torch.randn(tokens, heads, device=dev)
+    row_seq = torch.zeros(tokens, dtype=torch.int32, device=dev)
+    row_pos = torch.arange(tokens, dtype=torch.int32, device=dev)
+    seen = tokens * (tokens + 1) / 2 if tokens <= window else window * (window + 1) / 2 + (tokens - window) * window
+    fl = heads * 2 * (dim + dim) * seen
+
+    def product_frac(name, fn):
+        ms = _median_ms(torch, fn, 10, flush)
+        out[name] = {"us": round(ms * 1e3, 1), "frac_of_product_peak": round(fl / (ms * 1e-3) / peak, 4)}
+
+    product_frac("talk_attention_prompt", lambda: K.talk_attention(
+        qq, kk, vv, row_seq, row_pos, cu1, None, 0, 0, talk, gate, 0, oo, heads, kv, dim, dim, window,
+        dim ** -0.5))
+    product_frac("plain_attention_prompt_mma", lambda: K.sink_attention_mma(
+        qq, kk, vv, cu1, None, None, 0, 0, oo, None, None, 1, tokens, heads, kv, dim, dim, window, 0,
+        False, dim ** -0.5))
+    product_frac("plain_attention_prompt_tcgen05", lambda: K.attention_prefill_tc(
+        qq, kk, vv, cu1, oo, 1, tokens, heads, kv, dim, window, dim ** -0.5, status))
+    n_pages = batch * (tokens // 64)
+    kc = (torch.randn(n_pages, kv, 64, dim, device=dev) * 0.5).to(bf)
+    vc = torch.randn(n_pages, kv, 64, dim, device=dev).to(bf)
+    table = torch.arange(n_pages, dtype=torch.int32, device=dev)
+    rows_i = torch.arange(batch, dtype=torch.int32, device=dev)
+    pos = torch.full((batch,), tokens - 1, dtype=torch.int32, device=dev)
+    q1 = (torch.randn(batch, heads, dim, device=dev) * 0.5).to(bf)
+    o1 = torch.empty(batch, heads * dim, dtype=bf, device=dev)
+    reach = min(tokens, window)
+    nbytes = batch * kv * reach * 2 * dim * 2
+    timed("talk_attention_decode", lambda: K.talk_attention(
+        q1, kc, vc, rows_i, pos, None, table, tokens // 64, 0, talk, gate, 0, o1, heads, kv, dim, dim,
+        window, dim ** -0.5, reach_keys=reach), nbytes)
+    timed("plain_attention_decode_mma", lambda: K.sink_attention_decode(
+        q1, kc, vc, rows_i, pos, table, tokens // 64, 0, o1, None, None, heads, kv, dim, dim, window, 0,
+        False, dim ** -0.5, reach), nbytes)
+    return out
+
+
+def workload_bedarax(args) -> int:
+    """Prefill of one 2,048-token prompt and decoding at batch 8 from 2,048-token contexts, for
+    the Bedarax design (delta-rule, talking-attention and channel-wise delta-rule layers with
+    routed and dense feed-forwards) and for the Qwen2 decoder at equal width, heads, feed-forward
+    width and layers, random weights, bfloat16; and the design's kernels alone."""
+    import torch
+    from minfer_b200.engine.generate import Generator
+    from minfer_b200.kernels import api as K
+    from minfer_b200.model import Model
+    pk, pk_kind = peaks()
+    torch.cuda.set_device(0)
+    steps = max(8, min(args.steps, 128))
+    clocks = ClockSampler()
+    clocks.start()
+    t_all = time.time()
+    sizes = []
+    for name, width, heads, kv, dim, ff, rec_heads, rec_kv, window, experts, top in BEDARAX_SIZES:
+        cfg_b = bedarax_config(width, heads, kv, dim, ff, rec_heads, rec_kv, window, experts, top,
+                               FURITAR_VOCAB)
+        cfg_q = dict(CONFIG_7B, vocab_size=FURITAR_VOCAB, hidden_size=width,
+                     num_hidden_layers=BEDARAX_LAYERS, num_attention_heads=heads,
+                     num_key_value_heads=kv, intermediate_size=ff, max_position_embeddings=CONTEXT)
+        entry = {"name": name, "width": width, "heads": heads, "kv_heads": kv, "head_size": dim,
+                 "feed_forward": ff, "recurrent_heads": rec_heads, "recurrent_qk_heads": rec_kv,
+                 "window": window, "experts": experts, "experts_a_token": top,
+                 "layers": BEDARAX_LAYERS}
+        for label, cfg in (("bedarax", cfg_b), ("qwen2", cfg_q)):
+            model = Model.from_config(cfg, seed=0, dtype="bfloat16", device="cuda:0", make_on="device")
+            gen = Generator(model, max_tokens=BATCH * CONTEXT, max_batch=BATCH)
+            engine = gen.engine
+            g = torch.Generator().manual_seed(2)
+            ids = torch.randint(0, FURITAR_VOCAB, (PROMPT,), generator=g).tolist()
+            ms_prefill = time_prefill(engine, torch, ids, 10)
+            flops = bedarax_prefill_flops(cfg, PROMPT) if label == "bedarax" else prefill_flops(cfg, PROMPT)
+            ms_step, launched = time_decode(engine, torch, K, BATCH, steps, max(3, args.warmup), PROMPT)
+            ms_med = time_decode.median_ms
+            context = PROMPT + 3 + steps / 2
+            step_bytes = (bedarax_decode_bytes(model, cfg, BATCH, context) if label == "bedarax"
+                          else decode_bytes(model, BATCH, context))
+            entry[label] = {
+                "weights_gb": round(model.parameter_bytes() / 1e9, 3),
+                "prefill_tokens_per_s": round(PROMPT * 1e3 / ms_prefill, 1),
+                "prefill_ms": round(ms_prefill, 3),
+                "prefill_frac": round(flops / (ms_prefill * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                "decode_tokens_per_s": round(BATCH * 1e3 / ms_med, 1),
+                "decode_ms_per_step": round(ms_med, 4), "decode_frac": _frac(step_bytes, ms_med, pk),
+                "decode_launches_per_step": round(launched / steps, 1)}
+            del gen, engine, model
+            torch.cuda.empty_cache()
+        entry["kernels"] = bedarax_kernels(torch, K, pk, width, heads, kv, dim, ff, rec_heads, rec_kv,
+                                           window, experts, top)
+        sizes.append(entry)
+    summary = clocks.summary((t_all, time.time()))
+    clocks.stop()
+    print(json.dumps({
+        "workload": "bedarax", "impl": "ours", "dtype": "bf16", "data": "synthetic", "n_gpus": 1,
+        "metric": "prefill tokens/s of one 2048-token prompt and decode tokens/s at batch 8 from "
+                  "2048-token contexts, Bedarax beside Qwen2 at equal width and layers",
+        "unit": "tokens/s", "steps": steps, "prompt_len": PROMPT, "batch": BATCH,
+        "fractions": f"prefill: flops over the {pk_kind} bf16 product peak; decode: bytes of the "
+                     f"weights a step can touch, the visible cache and the recurrent state over "
+                     f"the {pk_kind} copy bandwidth",
+        "l2": "weights larger than L2 are read every step; kernels alone: L2 flushed before each run",
+        "clocks": summary, "sizes": sizes}))
+    return 0
+
+
 REF_KERNELS = os.path.join(ROOT, "baseline", "_ref", "libref_kernels.so")
 # the reference's checkout, if it sits beside this repository (or where MINFER_REFERENCE_DIR says)
 REF_SOURCE = os.path.join(os.environ.get("MINFER_REFERENCE_DIR",
@@ -895,7 +1172,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None,
                     help="run fewer layers than the configuration has (both numbers are reported)")
-    ap.add_argument("--workload", default="qwen2-7b", choices=["qwen2-7b", "furitar", "budanex"],
+    ap.add_argument("--workload", default="qwen2-7b", choices=["qwen2-7b", "furitar", "budanex", "bedarax"],
                     help="qwen2-7b (the default): the headline figure and its points; furitar: "
                          "the Furitar design beside Qwen2 at equal sizes, prefill and decode")
     ap.add_argument("--skip-points", action="store_true",
@@ -916,6 +1193,8 @@ def main() -> int:
         return workload_furitar(args)
     if args.workload == "budanex":
         return workload_budanex(args)
+    if args.workload == "bedarax":
+        return workload_bedarax(args)
 
     import torch
     from minfer_b200.engine.generate import Generator
