@@ -926,6 +926,9 @@ def bedarax_kernels(torch, K, pk, width, heads, kv, dim, ff, rec_heads, rec_kv, 
 
     product_frac("talk_attention_prompt", lambda: K.talk_attention(
         qq, kk, vv, row_seq, row_pos, cu1, None, 0, 0, talk, gate, 0, oo, heads, kv, dim, dim, window,
+        dim ** -0.5, q_cu_seqlens=cu1, n_seq=1, max_row_tokens=tokens))
+    product_frac("talk_attention_prompt_a_query_a_block", lambda: K.talk_attention(
+        qq, kk, vv, row_seq, row_pos, cu1, None, 0, 0, talk, gate, 0, oo, heads, kv, dim, dim, window,
         dim ** -0.5))
     product_frac("plain_attention_prompt_mma", lambda: K.sink_attention_mma(
         qq, kk, vv, cu1, None, None, 0, 0, oo, None, None, 1, tokens, heads, kv, dim, dim, window, 0,

@@ -212,7 +212,9 @@ def _sig_mixer_prep(lib: ctypes.CDLL) -> None:
 
 
 def _sig_delta_rule(lib: ctypes.CDLL) -> None:
-    lib.mf_delta_scan.argtypes = [c_void_p, c_int, c_void_p]
+    lib.mf_delta_scan.argtypes = [c_void_p, c_int, c_int, c_void_p]
+    lib.mf_delta_prep_width.argtypes = [c_int, c_int, c_int, c_int]
+    lib.mf_delta_prep_width.restype = c_int
     lib.mf_head_norm_gate.argtypes = [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p,
                                       c_int, c_int, c_int, c_int, c_float, c_int, c_void_p]
 
@@ -221,6 +223,8 @@ def _sig_attention_talk(lib: ctypes.CDLL) -> None:
     lib.mf_talk_attention.argtypes = [c_void_p, c_int, c_int, c_void_p]
     lib.mf_talk_attention_scratch.argtypes = [c_int, c_int, c_int, c_int]
     lib.mf_talk_attention_scratch.restype = c_longlong
+    lib.mf_talk_attention_tile.argtypes = [c_void_p, c_int, c_void_p]
+    lib.mf_talk_tile_cluster.argtypes = [c_int, c_int, c_int, c_int]
     lib.mf_value_mix.argtypes = [c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_int, c_void_p,
                                  c_int, c_int, c_void_p]
 
@@ -1003,8 +1007,8 @@ class _DeltaArgs(ctypes.Structure):
                 ("beta_off", c_int), ("decay", c_void_p), ("decay_width", c_longlong),
                 ("decay_off", c_int), ("dt_bias", c_void_p), ("a_log", c_void_p),
                 ("state", c_void_p), ("cu_seqlens", c_void_p), ("slots", c_void_p),
-                ("out", c_void_p)] + [(n, c_int) for n in ("n_rows", "heads", "kv_heads", "D", "Dv",
-                                                            "per_channel")]
+                ("out", c_void_p), ("prep", c_void_p), ("prep_width", c_longlong)] + [
+                    (n, c_int) for n in ("n_rows", "heads", "kv_heads", "D", "Dv", "per_channel")]
 
 
 def delta_scan(u: torch.Tensor, q_off: int, k_off: int, v_off: int, beta: torch.Tensor,
@@ -1018,7 +1022,9 @@ def delta_scan(u: torch.Tensor, q_off: int, k_off: int, v_off: int, beta: torch.
     ``decay_off + h * key_dim + d`` with ``per_channel``).  q and k become unit vectors per head,
     q times key_dim^(-1/2); g = exp(-exp(a_log[h]) softplus(raw + dt_bias)); S <- g S;
     u = sigmoid(beta) (v - S^T k); S <- S + k u^T; out = S^T q.  ``state`` float32
-    [slots, heads, value_dim, key_dim] goes on from what the row's slot holds."""
+    [slots, heads, value_dim, key_dim] goes on from what the row's slot holds.  When a row may
+    bring several tokens, what does not depend on the state (unit vectors, q . k, beta, decays) is
+    prepared for all tokens by a kernel of its own and the scan streams it."""
     n = u.shape[0]
     n_decay = heads * key_dim if per_channel else heads
     if (out.shape != (n, heads * value_dim) or state.shape[1:] != (heads, value_dim, key_dim)
@@ -1037,8 +1043,13 @@ def delta_scan(u: torch.Tensor, q_off: int, k_off: int, v_off: int, beta: torch.
     a.out = _f32(out, "out")
     a.n_rows, a.heads, a.kv_heads, a.D, a.Dv = int(n_rows), heads, kv_heads, key_dim, value_dim
     a.per_channel = 1 if per_channel else 0
-    _check(_lib("delta_rule").mf_delta_scan(ctypes.addressof(a), int(max_row_tokens), _stream()),
-           "delta_scan")
+    prep = None
+    if max_row_tokens > 1:
+        width = _lib("delta_rule").mf_delta_prep_width(heads, kv_heads, key_dim, a.per_channel)
+        prep = torch.empty((n, width), dtype=torch.float32, device=u.device)
+    a.prep, a.prep_width = _f32(prep, "prep"), prep.shape[1] if prep is not None else 0
+    _check(_lib("delta_rule").mf_delta_scan(ctypes.addressof(a), int(max_row_tokens), n, _stream()),
+           "delta_scan", 2 if prep is not None else 1)
 
 
 HEAD_GATES = {"silu": 0, "sigmoid": 1}
@@ -1068,16 +1079,23 @@ class _TalkArgs(ctypes.Structure):
                  ("gate_width", c_longlong), ("gate_off", c_int), ("out", c_void_p),
                  ("scratch", c_void_p)] +
                 [(n, c_int) for n in ("rows", "heads", "n_kv", "hd", "vd", "window", "splits")] +
-                [("scale", c_float)])
+                [("scale", c_float), ("q_cu", c_void_p)] +
+                [(n, c_int) for n in ("n_seq", "max_q_tiles", "cluster", "nkv")])
 
 
 def talk_attention_splits(rows: int, reach_keys: int) -> int:
     """Stretches a query's keys are cut into: enough blocks to fill the GPU when the queries are
-    few and their keys many (at least 128 keys a stretch)."""
+    few and their keys many (at least a tile of 32 keys a stretch)."""
     if rows <= 0:
         return 1
-    want = max(1, (2 * 148) // rows)
-    return max(1, min(want, reach_keys // 128, 32))
+    want = max(1, (4 * 148) // rows)
+    return max(1, min(want, reach_keys // 32, 32))
+
+
+def talk_tile_cluster(n_heads: int, n_kv: int, head_dim: int, value_dim: int) -> int:
+    """Blocks of the cluster that the tiled kernel of talking attention runs a tile of 16 queries
+    on for this shape (each block a share of the heads); 0: the shape is not taken."""
+    return int(_lib("attention_talk").mf_talk_tile_cluster(n_heads, n_kv, head_dim, value_dim))
 
 
 def talk_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, row_seq: torch.Tensor,
@@ -1085,19 +1103,27 @@ def talk_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, row_seq: t
                    page_table: Optional[torch.Tensor], table_stride: int, ring: int,
                    talk: torch.Tensor, gate: Optional[torch.Tensor], gate_off: int,
                    out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, value_dim: int,
-                   window: int, scale: float, reach_keys: int = 0) -> None:
+                   window: int, scale: float, reach_keys: int = 0,
+                   q_cu_seqlens: Optional[torch.Tensor] = None, n_seq: int = 0,
+                   max_row_tokens: int = 0) -> None:
     """Softmax attention with s'_h = sum_g talk[h][g] (q_g . k) * scale, causal with an optional
     window, over the step's packed keys (``page_table`` None: key j of batch row b at token
     cu_seqlens[b] + j) or over the cache's pages; head h's output times sigmoid(gate[row][gate_off
     + h]) if ``gate`` (float32 rows) is given.  ``reach_keys``: a bound on the keys a query sees,
-    used to cut long stretches over several blocks."""
+    used to cut long stretches over several blocks.  With ``q_cu_seqlens`` (the queries of batch row
+    b are rows q_cu_seqlens[b] .. q_cu_seqlens[b + 1], at consecutive positions), ``n_seq`` batch rows
+    and ``max_row_tokens`` > 1, bfloat16 inputs of a shape the tiled kernel takes run as tiles of 16
+    queries on the tensor cores, the heads spread over a thread-block cluster."""
     rows = q.shape[0]
     paged = page_table is not None
+    tiled = (q_cu_seqlens is not None and n_seq > 0 and max_row_tokens > 1
+             and q.dtype == torch.bfloat16
+             and talk_tile_cluster(n_heads, n_kv, head_dim, value_dim) > 0)
     if out.shape != (rows, n_heads * value_dim) or talk.shape != (n_heads, n_heads):
         raise KernelError("talk_attention: shapes do not fit")
     if k.dtype != q.dtype or v.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelError("talk_attention: q, k, v and the output must share one dtype")
-    splits = talk_attention_splits(rows, reach_keys) if reach_keys > 0 else 1
+    splits = talk_attention_splits(rows, reach_keys) if reach_keys > 0 and not tiled else 1
     scratch = None
     if splits > 1:
         scratch = torch.empty(rows * splits * n_heads * (value_dim + 2), dtype=torch.float32,
@@ -1112,6 +1138,12 @@ def talk_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, row_seq: t
     a.gate_off, a.out, a.scratch = int(gate_off), _ptr(out, "out"), _f32(scratch, "scratch")
     a.rows, a.heads, a.n_kv, a.hd, a.vd = rows, n_heads, n_kv, head_dim, value_dim
     a.window, a.splits, a.scale = int(window), splits, float(scale)
+    if tiled:
+        a.q_cu, a.n_seq = _i32(q_cu_seqlens, "q_cu_seqlens"), int(n_seq)
+        a.max_q_tiles = (int(max_row_tokens) + 15) // 16
+        _check(_lib("attention_talk").mf_talk_attention_tile(ctypes.addressof(a), 1 if paged else 0,
+                                                             _stream()), "talk_attention_tile")
+        return
     _check(_lib("attention_talk").mf_talk_attention(ctypes.addressof(a), 1 if paged else 0,
                                                     dtype_code(q.dtype), _stream()),
            "talk_attention", 2 if splits > 1 else 1)

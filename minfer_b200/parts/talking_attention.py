@@ -167,7 +167,8 @@ class TalkingAttention(Mixer):
         if own_kv:
             K.talk_attention(q, k_step, v_step, ctx.token_row, ctx.positions, ctx.cu_seqlens, None,
                              0, 0, self.talk_w, gate, gate_off, o, nh, nk, hd, vd, self.window,
-                             self.scale)
+                             self.scale, q_cu_seqlens=ctx.cu_seqlens, n_seq=ctx.n_rows,
+                             max_row_tokens=ctx.max_row_tokens)
         else:
             if cache.ring and ctx.max_row_tokens > cache.ring - self.window + 1:
                 raise K.KernelError(
@@ -177,5 +178,7 @@ class TalkingAttention(Mixer):
             reach = min(self.window, ctx.max_end) if self.window > 0 else ctx.max_end
             K.talk_attention(q, cache.k, cache.v, ctx.token_row, ctx.positions, None,
                              cache.page_table, cache.table_stride, cache.ring, self.talk_w, gate,
-                             gate_off, o, nh, nk, hd, vd, self.window, self.scale, reach_keys=reach)
+                             gate_off, o, nh, nk, hd, vd, self.window, self.scale, reach_keys=reach,
+                             q_cu_seqlens=ctx.cu_seqlens, n_seq=ctx.n_rows,
+                             max_row_tokens=ctx.max_row_tokens)
         project_out(self.out, o, ctx, residual)

@@ -111,6 +111,78 @@ def test_talking_attention_over_the_cache(dtype, window, standout, ring):
         assert err < _tol(dtype) * float(want.abs().max()), (rows, err)
 
 
+TILE_SHAPES = [(4, 2, 32, 40), (8, 2, 16, 24), (16, 8, 16, 16), (32, 4, 16, 8), (6, 3, 48, 16),
+               (2, 1, 16, 8), (12, 4, 32, 32)]
+
+
+@pytest.mark.parametrize("window, standout", [(0, 3), (70, 0), (70, 1), (64, 0), (33, 0), (32, 1),
+                                              (1, 0), (136, 1), (200, 150)])
+@pytest.mark.parametrize("H, G, D, Dv", TILE_SHAPES)
+def test_talking_attention_tiles_of_queries_over_a_prompt(window, standout, H, G, D, Dv):
+    """Every query of a 300-token prompt and of a 21-token prompt beside it through the tiled
+    kernel: clusters of 1 to 8 blocks, heads a block that are fewer, as many and more than a
+    key/value head serves."""
+    from minfer_b200.kernels import api as K
+    dtype = torch.bfloat16
+    assert K.talk_tile_cluster(H, G, D, Dv) > 0
+    n, m = 300, 21
+    q, k, v = _standout(n, H, G, D, Dv, window, standout, dtype, window * 3 + standout + H)
+    q2, k2, v2 = _standout(m, H, G, D, Dv, min(window, m), 0, dtype, 11)
+    talk = torch.eye(H, dtype=torch.float64) * 0.6 + torch.randn(H, H, dtype=torch.float64) * 0.5
+    talk = talk.to(torch.float32).to(torch.float64)
+    gate = torch.randn(n + m, H + 2, dtype=torch.float32)
+    want = torch.cat([P.talking_attention(q, k, v, talk, list(range(n)), 0.4, window),
+                      P.talking_attention(q2, k2, v2, talk, list(range(m)), 0.4, window)])
+    want = want * torch.sigmoid(gate[:, 2:].to(torch.float64)).unsqueeze(-1)
+    out = torch.empty((n + m, H * Dv), dtype=dtype, device=DEV)
+    cu = _i32([0, n, n + m])
+    K.talk_attention(torch.cat([q, q2]).to(dtype).to(DEV), torch.cat([k, k2]).to(dtype).to(DEV),
+                     torch.cat([v, v2]).to(dtype).to(DEV), _i32([0] * n + [1] * m),
+                     _i32(list(range(n)) + list(range(m))), cu, None, 0, 0,
+                     talk.to(torch.float32).to(DEV), gate.to(DEV), 2, out, H, G, D, Dv, window, 0.4,
+                     q_cu_seqlens=cu, n_seq=2, max_row_tokens=n)
+    got = out.cpu().to(torch.float64).view(n + m, H, Dv)
+    err = (got - want).abs().amax(dim=(1, 2))
+    assert float(err.max()) < _tol(dtype) * float(want.abs().max()), (int(err.argmax()), float(err.max()))
+
+
+@pytest.mark.parametrize("window, standout", [(0, 3), (70, 0), (70, 1), (64, 0), (65, 0), (136, 1)])
+@pytest.mark.parametrize("ring", [0, 1])
+@pytest.mark.parametrize("H, G, D, Dv", [(4, 2, 32, 40), (16, 4, 16, 16)])
+def test_talking_attention_tiles_of_queries_over_the_cache(window, standout, ring, H, G, D, Dv):
+    """A portion of a prompt over pages (scrambled; a ring that has wrapped): the last 2, 17 and
+    51 positions of 600 as one row's queries, beside a row that brings one token."""
+    from minfer_b200.kernels import api as K
+    dtype = torch.bfloat16
+    n = 600
+    if ring and not window:
+        pytest.skip("a ring belongs to a window")
+    q, k, v = _standout(n, H, G, D, Dv, window, standout, dtype, window * 5 + standout)
+    talk = (torch.eye(H) * 0.6 + torch.randn(H, H) * 0.5).to(torch.float64)
+    for portion in (2, 17, 51):
+        ring_len = ((window + portion + 63) // 64) * 64 if ring else 0
+        if ring_len >= n:
+            ring_len = 0
+        kc, vc, table = _paged(k, v, dtype, ring_len)
+        rows = list(range(n - portion, n))
+        other = n - 7                       # a second row: the same sequence seen at one position
+        want = P.talking_attention(q[[other] + rows], k, v, talk, [other] + rows, 0.4, window)
+        if ring_len and other - window + 1 < n - ring_len:
+            want[0] = float("nan")          # the ring has dropped keys this position would see
+        out = torch.empty((portion + 1, H * Dv), dtype=dtype, device=DEV)
+        cu = _i32([0, 1, portion + 1])
+        tables = torch.stack([table, table])
+        K.talk_attention(q[[other] + rows].to(dtype).to(DEV).contiguous(), kc, vc,
+                         _i32([0] + [1] * portion), _i32([other] + rows), None, tables,
+                         table.numel(), ring_len, talk.to(torch.float32).to(DEV), None, 0, out,
+                         H, G, D, Dv, window, 0.4, reach_keys=min(window, n) if window else n,
+                         q_cu_seqlens=cu, n_seq=2, max_row_tokens=portion)
+        got = out.cpu().to(torch.float64).view(portion + 1, H, Dv)
+        keep = ~torch.isnan(want[:, 0, 0])
+        err = float((got[keep] - want[keep]).abs().max())
+        assert err < _tol(dtype) * float(want[keep].abs().max()), (portion, err)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_talking_attention_two_sequences_and_an_identity_mix(dtype):
     """Two packed prompts of unequal length: a query never sees the other prompt's keys; with the
