@@ -64,7 +64,7 @@ struct TalkArgs {
     // the tiled kernel only: the queries' row starts, the rows, the most 16-query tiles a row has,
     // the cluster's size and the most key/value heads one block of it reads
     const int* q_cu;
-    int n_seq, max_q_tiles, cluster, nkv;
+    int n_seq, max_q_tiles, cluster, nkv, raw_bufs;
 };
 
 template <typename T, bool PAGED, bool VEC, int NACC>
@@ -375,7 +375,7 @@ extern "C" int mf_value_mix(float* v, long long v_width, int v_off, const float*
 #define TT_THREADS 128
 #define TT_WARPS 4
 #define TT_MAX_NT 16            // tiles of 8 output columns a warp may own
-#define TT_RAW_LD (TT_BN + 4)   // floats
+#define TT_RAW_LD (TT_BN + 8)   // floats: rows 8 banks apart, so a half warp's float2 stores do not collide
 #define TT_P_LD (TT_BN + 8)     // bfloat16
 #define TT_MAX_SMEM (200 * 1024)
 
@@ -409,7 +409,7 @@ __device__ __forceinline__ uint32_t tt_mapa(uint32_t addr, uint32_t rank) {
 __device__ __forceinline__ float4 tt_ld_cluster(uint32_t addr) {
     float4 v;
     asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
     return v;
 }
 __device__ __forceinline__ void tt_cluster_sync() {
@@ -418,42 +418,46 @@ __device__ __forceinline__ void tt_cluster_sync() {
 }
 
 // bytes of shared memory a block needs
-__host__ __device__ inline size_t talk_tile_smem(int H, int cs, int nkv, int hd, int vd) {
+__host__ __device__ inline size_t talk_tile_smem(int H, int cs, int nkv, int hd, int vd, int raw_bufs) {
     const size_t hpc = H / cs, hpcp = (hpc + 3) & ~(size_t)3;
     size_t b = hpc * TT_BM * (hd + 8) * 2;                       // queries
     b += 2 * (size_t)nkv * TT_BN * (hd + 8) * 2;                 // keys, two stages
     b += 2 * (size_t)nkv * TT_BN * (vd + 8) * 2;                 // values, two stages
     b += hpc * TT_BM * TT_P_LD * 2;                              // weights
-    b += 2 * hpc * TT_BM * TT_RAW_LD * 4;                        // raw scores, two buffers
+    b += raw_bufs * hpc * TT_BM * TT_RAW_LD * 4;                 // raw scores, one or two buffers
     b += (size_t)H * hpcp * 4;                                   // the own heads' rows of T, transposed
     b += 3 * hpc * TT_BM * 4;                                    // max, sum, correction
     b += TT_BM * 4 + 2 * TT_BN * 8;                              // positions, key bases
+    b += hpcp * 4;                                               // the own heads' key/value heads
     return b;
 }
 
-template <bool PAGED>
+// HPC_T: the heads a block owns when known at compile time (4, the usual share), else 0
+template <bool PAGED, int HPC_T>
 __global__ void __launch_bounds__(TT_THREADS) talk_tile_kernel(TalkArgs a) {
     pdl_launch_dependents();
     extern __shared__ __align__(16) unsigned char tt_smem[];
     typedef __nv_bfloat16 bf16;
     const int H = a.heads, G = a.n_kv, R = H / G, hd = a.hd, vd = a.vd;
-    const int CS = a.cluster, HPC = H / CS, HPCP = (HPC + 3) & ~3, NKV = a.nkv;
+    const int CS = a.cluster, HPC = HPC_T ? HPC_T : H / CS, HPCP = (HPC + 3) & ~3, NKV = a.nkv;
     const int q_ld = hd + 8, v_ld = vd + 8;
     bf16* q_s = reinterpret_cast<bf16*>(tt_smem);                      // [HPC][16][q_ld]
     bf16* k_s = q_s + (size_t)HPC * TT_BM * q_ld;                      // [2][NKV][32][q_ld]
     bf16* v_s = k_s + 2 * (size_t)NKV * TT_BN * q_ld;                  // [2][NKV][32][v_ld]
     bf16* p_s = v_s + 2 * (size_t)NKV * TT_BN * v_ld;                  // [HPC][16][TT_P_LD]
     float* raw_s = reinterpret_cast<float*>(p_s + (size_t)HPC * TT_BM * TT_P_LD);   // [2][HPC][16][TT_RAW_LD]
-    float* tt_s = raw_s + 2 * (size_t)HPC * TT_BM * TT_RAW_LD;         // [H][HPCP]: T[h0 + hl][g] * scale
+    float* tt_s = raw_s + (size_t)a.raw_bufs * HPC * TT_BM * TT_RAW_LD;   // [H][HPCP]: T[h0 + hl][g] * scale
     float* m_s = tt_s + (size_t)H * HPCP;                              // [HPC][16]
     float* l_s = m_s + HPC * TT_BM;
     float* alpha_s = l_s + HPC * TT_BM;
     int* pos_s = reinterpret_cast<int*>(alpha_s + HPC * TT_BM);        // [16]
     long long* base_s = reinterpret_cast<long long*>(pos_s + TT_BM);   // [2][32], -1: not visible
+    int* kvh_s = reinterpret_cast<int*>(base_s + 2 * TT_BN);           // [HPC] key/value head - c_lo
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int rank = blockIdx.x;                      // the cluster runs along x and is the grid's x
-    const int tile = blockIdx.y / a.splits, split = blockIdx.y - tile * a.splits;
+    // the last tiles of a row see the most keys: they start first
+    const int tile = a.max_q_tiles - 1 - blockIdx.y / a.splits, split = blockIdx.y % a.splits;
     const int b = blockIdx.z;
     const int h0 = rank * HPC;
     const int c_lo = h0 / R, c_hi = (h0 + HPC - 1) / R;
@@ -463,6 +467,7 @@ __global__ void __launch_bounds__(TT_THREADS) talk_tile_kernel(TalkArgs a) {
         tt_s[i] = hl < HPC ? a.talk[(size_t)(h0 + hl) * H + g] * a.scale : 0.f;
     }
     for (int i = tid; i < HPC * TT_BM; i += TT_THREADS) { m_s[i] = -INFINITY; l_s[i] = 0.f; alpha_s[i] = 0.f; }
+    for (int i = tid; i < HPC; i += TT_THREADS) kvh_s[i] = (h0 + i) / R - c_lo;
     pdl_wait();
     const int q0 = a.q_cu[b] + tile * TT_BM, q_end = a.q_cu[b + 1];
     if (q0 >= q_end) return;                          // the whole cluster leaves
@@ -509,21 +514,17 @@ __global__ void __launch_bounds__(TT_THREADS) talk_tile_kernel(TalkArgs a) {
         const long long* bs = base_s + stage * TT_BN;
         const int nkv_here = c_hi - c_lo + 1;
         const int c8 = hd >> 3, cv8 = vd >> 3;
-        for (int idx = tid; idx < nkv_here * TT_BN * c8; idx += TT_THREADS) {
-            const int cl = idx / (TT_BN * c8), rem = idx - cl * TT_BN * c8;
-            const int jj = rem / c8, ch = rem - jj * c8;
+        // a row of keys and of values a warp at a time, its 16-byte pieces over the lanes
+        for (int r = warp; r < nkv_here * TT_BN; r += TT_WARPS) {
+            const int cl = r / TT_BN, jj = r - cl * TT_BN;
             const long long base = bs[jj];
-            const bf16* src = base >= 0 ? kbase + (base + (c_lo + cl) * head_rows) * hd + ch * 8 : kbase;
-            tt_cp16(tt_u32(k_s + (((size_t)stage * NKV + cl) * TT_BN + jj) * q_ld + ch * 8), src,
-                    base >= 0 ? 16 : 0);
-        }
-        for (int idx = tid; idx < nkv_here * TT_BN * cv8; idx += TT_THREADS) {
-            const int cl = idx / (TT_BN * cv8), rem = idx - cl * TT_BN * cv8;
-            const int jj = rem / cv8, ch = rem - jj * cv8;
-            const long long base = bs[jj];
-            const bf16* src = base >= 0 ? vbase + (base + (c_lo + cl) * head_rows) * vd + ch * 8 : vbase;
-            tt_cp16(tt_u32(v_s + (((size_t)stage * NKV + cl) * TT_BN + jj) * v_ld + ch * 8), src,
-                    base >= 0 ? 16 : 0);
+            const int bytes = base >= 0 ? 16 : 0;
+            const bf16* ksrc = base >= 0 ? kbase + (base + (c_lo + cl) * head_rows) * hd : kbase;
+            const bf16* vsrc = base >= 0 ? vbase + (base + (c_lo + cl) * head_rows) * vd : vbase;
+            const uint32_t kd = tt_u32(k_s + (((size_t)stage * NKV + cl) * TT_BN + jj) * q_ld);
+            const uint32_t vdst = tt_u32(v_s + (((size_t)stage * NKV + cl) * TT_BN + jj) * v_ld);
+            for (int ch = lane; ch < c8; ch += 32) tt_cp16(kd + ch * 16, base >= 0 ? ksrc + ch * 8 : ksrc, bytes);
+            for (int ch = lane; ch < cv8; ch += 32) tt_cp16(vdst + ch * 16, base >= 0 ? vsrc + ch * 8 : vsrc, bytes);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -531,6 +532,7 @@ __global__ void __launch_bounds__(TT_THREADS) talk_tile_kernel(TalkArgs a) {
     // the output sums: this warp's share of the block's (head, 8 columns) tiles
     const int NTV = vd >> 3, n_out = HPC * NTV, out_per = (n_out + TT_WARPS - 1) / TT_WARPS;
     const int out_first = warp * out_per, out_cnt = max(0, min(out_per, n_out - out_first));
+    const int out_hl0 = out_first / NTV, out_nt0 = out_first - out_hl0 * NTV;
     float o[TT_MAX_NT][4];
 #pragma unroll
     for (int u = 0; u < TT_MAX_NT; ++u) { o[u][0] = 0.f; o[u][1] = 0.f; o[u][2] = 0.f; o[u][3] = 0.f; }
@@ -542,6 +544,7 @@ __global__ void __launch_bounds__(TT_THREADS) talk_tile_kernel(TalkArgs a) {
     }
     for (int t = t_begin; t < t_end; ++t) {
         const int s = (t - t_begin) & 1;
+        const int sr = a.raw_bufs > 1 ? s : 0;           // the raw scores' buffer
         if (t + 1 < t_end && tid < TT_BN)
             base_s[(s ^ 1) * TT_BN + tid] = key_base(lo_t + (t + 1) * TT_BN + tid);
         asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -549,13 +552,14 @@ __global__ void __launch_bounds__(TT_THREADS) talk_tile_kernel(TalkArgs a) {
         if (t + 1 < t_end) issue(s ^ 1);
         // (1) raw scores of the own heads: a warp per head, 16 queries x 32 keys
         for (int hl = warp; hl < HPC; hl += TT_WARPS) {
-            const int cl = (h0 + hl) / R - c_lo;
+            const int cl = kvh_s[hl];
             float sc[4][4];
 #pragma unroll
             for (int n = 0; n < 4; ++n) { sc[n][0] = 0.f; sc[n][1] = 0.f; sc[n][2] = 0.f; sc[n][3] = 0.f; }
             const uint32_t qa = tt_u32(q_s + ((size_t)hl * TT_BM + (lane & 15)) * q_ld + (lane >> 4) * 8);
             const uint32_t ka = tt_u32(k_s + (((size_t)s * NKV + cl) * TT_BN + (lane >> 4) * 8 + (lane & 7)) * q_ld
                                        + ((lane >> 3) & 1) * 8);
+#pragma unroll 2
             for (int ks = 0; ks < (hd >> 4); ++ks) {
                 uint32_t af[4], b0[4], b1[4];
                 tt_ldsm(qa + ks * 32, af);
@@ -566,7 +570,7 @@ __global__ void __launch_bounds__(TT_THREADS) talk_tile_kernel(TalkArgs a) {
                 tt_mma(sc[2], af, b1[0], b1[1]);
                 tt_mma(sc[3], af, b1[2], b1[3]);
             }
-            float* rw = raw_s + ((size_t)s * HPC + hl) * TT_BM * TT_RAW_LD;
+            float* rw = raw_s + ((size_t)sr * HPC + hl) * TT_BM * TT_RAW_LD;
             const int r = lane >> 2, c = 2 * (lane & 3);
 #pragma unroll
             for (int n = 0; n < 4; ++n) {
@@ -586,7 +590,7 @@ __global__ void __launch_bounds__(TT_THREADS) talk_tile_kernel(TalkArgs a) {
                 const int j = jb + e;
                 vis[e] = i < nq && j <= pos_i && (a.window == 0 || pos_i - j < a.window);
             }
-            const uint32_t mine = tt_u32(raw_s + ((size_t)s * HPC * TT_BM + i) * TT_RAW_LD + 4 * jq);
+            const uint32_t mine = tt_u32(raw_s + ((size_t)sr * HPC * TT_BM + i) * TT_RAW_LD + 4 * jq);
             for (int hc = 0; hc < HPCP; hc += 4) {
                 float acc[4][4];
 #pragma unroll
@@ -594,6 +598,7 @@ __global__ void __launch_bounds__(TT_THREADS) talk_tile_kernel(TalkArgs a) {
                 for (int src = 0; src < CS; ++src) {
                     const uint32_t ra = tt_mapa(mine, (uint32_t)src);
                     const float* tt = tt_s + (size_t)src * HPC * HPCP + hc;
+#pragma unroll 4
                     for (int gl = 0; gl < HPC; ++gl) {
                         const float4 rv = tt_ld_cluster(ra + gl * TT_BM * TT_RAW_LD * 4);
                         const float4 tv = *reinterpret_cast<const float4*>(tt + gl * HPCP);
@@ -621,10 +626,10 @@ __global__ void __launch_bounds__(TT_THREADS) talk_tile_kernel(TalkArgs a) {
                         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
                         const float m_new = fmaxf(m_old, mx);
                         const float m_use = m_new == -INFINITY ? 0.f : m_new;   // no key seen yet
-                        const float corr = expf(m_old - m_use);
+                        const float corr = __expf(m_old - m_use);
                         float pv[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) pv[e] = expf(sv[e] - m_use);
+                        for (int e = 0; e < 4; ++e) pv[e] = __expf(sv[e] - m_use);
                         float sum = (pv[0] + pv[1]) + (pv[2] + pv[3]);
                         sum += __shfl_xor_sync(0xffffffffu, sum, 1);
                         sum += __shfl_xor_sync(0xffffffffu, sum, 2);
@@ -644,31 +649,52 @@ __global__ void __launch_bounds__(TT_THREADS) talk_tile_kernel(TalkArgs a) {
                 }
             }
         }
-        __syncthreads();
+        if (a.raw_bufs > 1) __syncthreads();
+        else tt_cluster_sync();           // one buffer: nobody may still read it when it is written again
         // (3) weights x values into the output sums
-        {
-            int cur = -1;
+        if (HPC_T == TT_WARPS && NTV == TT_MAX_NT) {
+            // the usual share: head `warp`, all 16 column tiles
+            uint32_t pa0[4], pa1[4];
+            const uint32_t pa = tt_u32(p_s + ((size_t)warp * TT_BM + (lane & 15)) * TT_P_LD + (lane >> 4) * 8);
+            tt_ldsm(pa, pa0);
+            tt_ldsm(pa + 32, pa1);
+            const float al0 = alpha_s[warp * TT_BM + (lane >> 2)];
+            const float al1 = alpha_s[warp * TT_BM + (lane >> 2) + 8];
+            const uint32_t v_head = tt_u32(v_s + (((size_t)s * NKV + kvh_s[warp]) * TT_BN + lane) * v_ld);
+#pragma unroll
+            for (int u = 0; u < TT_MAX_NT; ++u) {
+                uint32_t vb[4];
+                tt_ldsm_t(v_head + u * 16, vb);
+                o[u][0] *= al0; o[u][1] *= al0; o[u][2] *= al1; o[u][3] *= al1;
+                tt_mma(o[u], pa0, vb[0], vb[1]);
+                tt_mma(o[u], pa1, vb[2], vb[3]);
+            }
+        } else {
+            int cur = -1, hl = out_hl0, nt = out_nt0;
             uint32_t pa0[4], pa1[4];
             float al0 = 1.f, al1 = 1.f;
+            const uint32_t p_lane = tt_u32(p_s + (lane & 15) * TT_P_LD + (lane >> 4) * 8);
+            const uint32_t v_lane = tt_u32(v_s + ((size_t)s * NKV * TT_BN + lane) * v_ld);
+            const uint32_t v_head_bytes = (uint32_t)(TT_BN * v_ld * 2);
+            uint32_t v_head = v_lane;
 #pragma unroll
             for (int u = 0; u < TT_MAX_NT; ++u) {
                 if (u < out_cnt) {
-                    const int idx = out_first + u;
-                    const int hl = idx / NTV, nt = idx - hl * NTV;
                     if (hl != cur) {
-                        const uint32_t pa = tt_u32(p_s + ((size_t)hl * TT_BM + (lane & 15)) * TT_P_LD + (lane >> 4) * 8);
+                        const uint32_t pa = p_lane + (uint32_t)hl * (TT_BM * TT_P_LD * 2);
+                        v_head = v_lane + (uint32_t)kvh_s[hl] * v_head_bytes;
                         tt_ldsm(pa, pa0);
                         tt_ldsm(pa + 32, pa1);
                         al0 = alpha_s[hl * TT_BM + (lane >> 2)];
                         al1 = alpha_s[hl * TT_BM + (lane >> 2) + 8];
                         cur = hl;
                     }
-                    const int cl = (h0 + hl) / R - c_lo;
                     uint32_t vb[4];
-                    tt_ldsm_t(tt_u32(v_s + (((size_t)s * NKV + cl) * TT_BN + lane) * v_ld + nt * 8), vb);
+                    tt_ldsm_t(v_head + (uint32_t)nt * 16, vb);
                     o[u][0] *= al0; o[u][1] *= al0; o[u][2] *= al1; o[u][3] *= al1;
                     tt_mma(o[u], pa0, vb[0], vb[1]);
                     tt_mma(o[u], pa1, vb[2], vb[3]);
+                    if (++nt == NTV) { nt = 0; ++hl; }
                 }
             }
         }
@@ -676,11 +702,10 @@ __global__ void __launch_bounds__(TT_THREADS) talk_tile_kernel(TalkArgs a) {
     tt_cluster_sync();                    // nobody reads this block's raw scores any more
     {
         const int r = lane >> 2, c2 = 2 * (lane & 3);
+        int hl = out_hl0, nt = out_nt0;
 #pragma unroll
         for (int u = 0; u < TT_MAX_NT; ++u) {
             if (u < out_cnt) {
-                const int idx = out_first + u;
-                const int hl = idx / NTV, nt = idx - hl * NTV;
                 const int h = h0 + hl, col = nt * 8 + c2;
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
@@ -701,6 +726,7 @@ __global__ void __launch_bounds__(TT_THREADS) talk_tile_kernel(TalkArgs a) {
                         }
                     }
                 }
+                if (++nt == NTV) { nt = 0; ++hl; }
             }
         }
         if (a.splits > 1) {
@@ -731,7 +757,7 @@ static int talk_tile_cluster(int heads, int n_kv, int hd, int vd, int* nkv_out) 
         const int span = (r * hpc + hpc - 1) / R - (r * hpc) / R + 1;
         if (span > nkv) nkv = span;
     }
-    if (talk_tile_smem(heads, cs, nkv, hd, vd) > TT_MAX_SMEM) return 0;
+    if (talk_tile_smem(heads, cs, nkv, hd, vd, 1) > TT_MAX_SMEM) return 0;
     if (nkv_out) *nkv_out = nkv;
     return cs;
 }
@@ -741,11 +767,11 @@ extern "C" int mf_talk_tile_cluster(int heads, int n_kv, int hd, int vd) {
     return talk_tile_cluster(heads, n_kv, hd, vd, nullptr);
 }
 
-template <bool PAGED>
+template <bool PAGED, int HPC_T>
 static int talk_tile_launch(const TalkArgs& a, size_t smem, cudaStream_t stream) {
     static bool raised = false;          // once, outside any capture (a shape's first step)
     if (!raised) {
-        cudaFuncSetAttribute(talk_tile_kernel<PAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaFuncSetAttribute(talk_tile_kernel<PAGED, HPC_T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              TT_MAX_SMEM);
         raised = true;
     }
@@ -761,7 +787,7 @@ static int talk_tile_launch(const TalkArgs& a, size_t smem, cudaStream_t stream)
     attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    cudaLaunchKernelEx(&cfg, talk_tile_kernel<PAGED>, a);
+    cudaLaunchKernelEx(&cfg, talk_tile_kernel<PAGED, HPC_T>, a);
     if (a.splits > 1) {
         const long long n = (long long)a.rows * a.heads * a.vd;
         mf_launch(talk_combine_kernel<__nv_bfloat16>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0,
@@ -784,6 +810,16 @@ extern "C" int mf_talk_attention_tile(const TalkArgs* args, int paged, cudaStrea
     if ((long long)a.max_q_tiles * a.splits > 65535 || a.n_seq > 65535) return MF_ERR_UNSUPPORTED;
     a.cluster = cs;
     a.nkv = nkv;
-    const size_t smem = talk_tile_smem(a.heads, cs, nkv, a.hd, a.vd);
-    return paged ? talk_tile_launch<true>(a, smem, stream) : talk_tile_launch<false>(a, smem, stream);
+    // two buffers of raw scores save a cluster barrier a tile; one, when that lets another block
+    // live on the SM (three at most, by registers)
+    const size_t smem2 = talk_tile_smem(a.heads, cs, nkv, a.hd, a.vd, 2);
+    const size_t smem1 = talk_tile_smem(a.heads, cs, nkv, a.hd, a.vd, 1);
+    const size_t per_sm = 227 * 1024;
+    const size_t occ2 = smem2 > TT_MAX_SMEM ? 0 : (per_sm / (smem2 + 1024) < 3 ? per_sm / (smem2 + 1024) : 3);
+    const size_t occ1 = per_sm / (smem1 + 1024) < 3 ? per_sm / (smem1 + 1024) : 3;
+    a.raw_bufs = occ1 > occ2 ? 1 : 2;
+    const size_t smem = a.raw_bufs == 1 ? smem1 : smem2;
+    if (a.heads / cs == 4)
+        return paged ? talk_tile_launch<true, 4>(a, smem, stream) : talk_tile_launch<false, 4>(a, smem, stream);
+    return paged ? talk_tile_launch<true, 0>(a, smem, stream) : talk_tile_launch<false, 0>(a, smem, stream);
 }

@@ -1080,7 +1080,7 @@ class _TalkArgs(ctypes.Structure):
                  ("scratch", c_void_p)] +
                 [(n, c_int) for n in ("rows", "heads", "n_kv", "hd", "vd", "window", "splits")] +
                 [("scale", c_float), ("q_cu", c_void_p)] +
-                [(n, c_int) for n in ("n_seq", "max_q_tiles", "cluster", "nkv")])
+                [(n, c_int) for n in ("n_seq", "max_q_tiles", "cluster", "nkv", "raw_bufs")])
 
 
 def talk_attention_splits(rows: int, reach_keys: int) -> int:

@@ -112,7 +112,7 @@ def test_talking_attention_over_the_cache(dtype, window, standout, ring):
 
 
 TILE_SHAPES = [(4, 2, 32, 40), (8, 2, 16, 24), (16, 8, 16, 16), (32, 4, 16, 8), (6, 3, 48, 16),
-               (2, 1, 16, 8), (12, 4, 32, 32)]
+               (2, 1, 16, 8), (12, 4, 32, 32), (8, 2, 128, 128)]
 
 
 @pytest.mark.parametrize("window, standout", [(0, 3), (70, 0), (70, 1), (64, 0), (33, 0), (32, 1),
