@@ -945,7 +945,11 @@ def bedarax_kernels(torch, K, pk, width, heads, kv, dim, ff, rec_heads, rec_kv, 
     o1 = torch.empty(batch, heads * dim, dtype=bf, device=dev)
     reach = min(tokens, window)
     nbytes = batch * kv * reach * 2 * dim * 2
+    cu_b = torch.arange(batch + 1, dtype=torch.int32, device=dev)
     timed("talk_attention_decode", lambda: K.talk_attention(
+        q1, kc, vc, rows_i, pos, None, table, tokens // 64, 0, talk, gate, 0, o1, heads, kv, dim, dim,
+        window, dim ** -0.5, reach_keys=reach, q_cu_seqlens=cu_b, n_seq=batch, max_row_tokens=1), nbytes)
+    timed("talk_attention_decode_a_query_a_block", lambda: K.talk_attention(
         q1, kc, vc, rows_i, pos, None, table, tokens // 64, 0, talk, gate, 0, o1, heads, kv, dim, dim,
         window, dim ** -0.5, reach_keys=reach), nbytes)
     timed("plain_attention_decode_mma", lambda: K.sink_attention_decode(

@@ -1112,18 +1112,26 @@ def talk_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, row_seq: t
     + h]) if ``gate`` (float32 rows) is given.  ``reach_keys``: a bound on the keys a query sees,
     used to cut long stretches over several blocks.  With ``q_cu_seqlens`` (the queries of batch row
     b are rows q_cu_seqlens[b] .. q_cu_seqlens[b + 1], at consecutive positions), ``n_seq`` batch rows
-    and ``max_row_tokens`` > 1, bfloat16 inputs of a shape the tiled kernel takes run as tiles of 16
-    queries on the tensor cores, the heads spread over a thread-block cluster."""
+    and ``max_row_tokens``, bfloat16 inputs of a shape the tiled kernel takes run as tiles of 16
+    queries on the tensor cores, the heads spread over a thread-block cluster (few queries over
+    many keys: the key tiles dealt to several clusters and merged)."""
     rows = q.shape[0]
     paged = page_table is not None
-    tiled = (q_cu_seqlens is not None and n_seq > 0 and max_row_tokens > 1
-             and q.dtype == torch.bfloat16
-             and talk_tile_cluster(n_heads, n_kv, head_dim, value_dim) > 0)
+    cluster = (talk_tile_cluster(n_heads, n_kv, head_dim, value_dim)
+               if q_cu_seqlens is not None and n_seq > 0 and max_row_tokens >= 1
+               and q.dtype == torch.bfloat16 else 0)
+    tiled = cluster > 0
     if out.shape != (rows, n_heads * value_dim) or talk.shape != (n_heads, n_heads):
         raise KernelError("talk_attention: shapes do not fit")
     if k.dtype != q.dtype or v.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelError("talk_attention: q, k, v and the output must share one dtype")
-    splits = talk_attention_splits(rows, reach_keys) if reach_keys > 0 and not tiled else 1
+    if tiled:
+        # blocks of the tiled kernel: rows x tiles of 16 queries x the cluster; two key tiles a
+        # stretch at least
+        blocks = n_seq * ((int(max_row_tokens) + 15) // 16) * cluster
+        splits = max(1, min((3 * 148) // blocks, reach_keys // 64, 32)) if reach_keys > 0 else 1
+    else:
+        splits = talk_attention_splits(rows, reach_keys) if reach_keys > 0 else 1
     scratch = None
     if splits > 1:
         scratch = torch.empty(rows * splits * n_heads * (value_dim + 2), dtype=torch.float32,
@@ -1142,7 +1150,8 @@ def talk_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, row_seq: t
         a.q_cu, a.n_seq = _i32(q_cu_seqlens, "q_cu_seqlens"), int(n_seq)
         a.max_q_tiles = (int(max_row_tokens) + 15) // 16
         _check(_lib("attention_talk").mf_talk_attention_tile(ctypes.addressof(a), 1 if paged else 0,
-                                                             _stream()), "talk_attention_tile")
+                                                             _stream()), "talk_attention_tile",
+               2 if splits > 1 else 1)
         return
     _check(_lib("attention_talk").mf_talk_attention(ctypes.addressof(a), 1 if paged else 0,
                                                     dtype_code(q.dtype), _stream()),

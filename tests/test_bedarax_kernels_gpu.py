@@ -150,8 +150,9 @@ def test_talking_attention_tiles_of_queries_over_a_prompt(window, standout, H, G
 @pytest.mark.parametrize("ring", [0, 1])
 @pytest.mark.parametrize("H, G, D, Dv", [(4, 2, 32, 40), (16, 4, 16, 16)])
 def test_talking_attention_tiles_of_queries_over_the_cache(window, standout, ring, H, G, D, Dv):
-    """A portion of a prompt over pages (scrambled; a ring that has wrapped): the last 2, 17 and
-    51 positions of 600 as one row's queries, beside a row that brings one token."""
+    """A portion of a prompt over pages (scrambled; a ring that has wrapped): the last 1, 2, 17 and
+    51 positions of 600 as one row's queries, beside a row that brings one token; the key tiles
+    dealt to several clusters and merged."""
     from minfer_b200.kernels import api as K
     dtype = torch.bfloat16
     n = 600
@@ -159,7 +160,7 @@ def test_talking_attention_tiles_of_queries_over_the_cache(window, standout, rin
         pytest.skip("a ring belongs to a window")
     q, k, v = _standout(n, H, G, D, Dv, window, standout, dtype, window * 5 + standout)
     talk = (torch.eye(H) * 0.6 + torch.randn(H, H) * 0.5).to(torch.float64)
-    for portion in (2, 17, 51):
+    for portion in (1, 2, 17, 51):
         ring_len = ((window + portion + 63) // 64) * 64 if ring else 0
         if ring_len >= n:
             ring_len = 0
