@@ -595,6 +595,7 @@ __global__ void __launch_bounds__(TT_THREADS) talk_tile_kernel(TalkArgs a) {
                 float acc[4][4];
 #pragma unroll
                 for (int x = 0; x < 4; ++x) { acc[x][0] = 0.f; acc[x][1] = 0.f; acc[x][2] = 0.f; acc[x][3] = 0.f; }
+#pragma unroll 2
                 for (int src = 0; src < CS; ++src) {
                     const uint32_t ra = tt_mapa(mine, (uint32_t)src);
                     const float* tt = tt_s + (size_t)src * HPC * HPCP + hc;

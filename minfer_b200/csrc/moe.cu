@@ -98,15 +98,17 @@ moe_up_kernel(const TX* __restrict__ x, const TW* __restrict__ wg, const TW* __r
               TX* __restrict__ hidden, int width, int ff, int top) {
     pdl_launch_dependents();
     extern __shared__ float moe_x[];
-    const int pair = blockIdx.y;                   // token * top + choice
+    // pairs run along x, the fastest: the blocks of one tile of rows are placed together, so pairs
+    // that chose the same expert find its rows in L2
+    const int pair = blockIdx.x;                   // token * top + choice
     const int t = pair / top;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     pdl_wait();
     for (int i = threadIdx.x; i < width; i += blockDim.x) moe_x[i] = to_f32(x[(size_t)t * width + i]);
     const int e = idx[pair];
     __syncthreads();
-    const int f_end = min(ff, (int)(blockIdx.x + 1) * MOE_ROWS);
-    for (int f = blockIdx.x * MOE_ROWS + warp; f < f_end; f += n_warps) {
+    const int f_end = min(ff, (int)(blockIdx.y + 1) * MOE_ROWS);
+    for (int f = blockIdx.y * MOE_ROWS + warp; f < f_end; f += n_warps) {
         const size_t wrow = (size_t)e * w_expert + (size_t)f * w_row;
         const float g = warp_sum(moe_dot(wg + wrow, moe_x, width, lane));
         const float u = warp_sum(moe_dot(wu + wrow, moe_x, width, lane));
@@ -122,14 +124,14 @@ moe_down_kernel(const TX* __restrict__ hidden, const TW* __restrict__ wd, const 
                 const float* __restrict__ wts, float* __restrict__ h, int width, int ff, int top) {
     pdl_launch_dependents();
     extern __shared__ float moe_hid[];             // [top][ff]
-    const int t = blockIdx.y;
+    const int t = blockIdx.x;                      // tokens along x, as the pairs above
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     pdl_wait();
     for (int i = threadIdx.x; i < top * ff; i += blockDim.x)
         moe_hid[i] = to_f32(hidden[(size_t)t * top * ff + i]);
     __syncthreads();
-    const int c_end = min(width, (int)(blockIdx.x + 1) * MOE_COLS);
-    for (int c = blockIdx.x * MOE_COLS + warp; c < c_end; c += n_warps) {
+    const int c_end = min(width, (int)(blockIdx.y + 1) * MOE_COLS);
+    for (int c = blockIdx.y * MOE_COLS + warp; c < c_end; c += n_warps) {
         float sum = 0.f;
         for (int k = 0; k < top; ++k) {
             const int e = idx[(size_t)t * top + k];
@@ -151,8 +153,10 @@ extern "C" int mf_moe_experts(const void* x, int x_dtype, const void* wg, const 
     if (top < 1 || top > MOE_MAX_TOP) return MF_ERR_UNSUPPORTED;
     const size_t smem_up = (size_t)width * sizeof(float), smem_dn = (size_t)top * ff * sizeof(float);
     if (smem_up > 48 * 1024 || smem_dn > 48 * 1024) return MF_ERR_UNSUPPORTED;
-    dim3 grid_up((ff + MOE_ROWS - 1) / MOE_ROWS, n_tokens * top);
-    dim3 grid_dn((width + MOE_COLS - 1) / MOE_COLS, n_tokens);
+    if ((ff + MOE_ROWS - 1) / MOE_ROWS > 65535 || (width + MOE_COLS - 1) / MOE_COLS > 65535)
+        return MF_ERR_UNSUPPORTED;
+    dim3 grid_up(n_tokens * top, (ff + MOE_ROWS - 1) / MOE_ROWS);
+    dim3 grid_dn(n_tokens, (width + MOE_COLS - 1) / MOE_COLS);
 #define MF_MOE(TX, TW) \
     do { \
         mf_launch(moe_up_kernel<TX, TW>, grid_up, dim3(256), smem_up, stream, (const TX*)x, \
