@@ -1149,10 +1149,11 @@ def talk_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, row_seq: t
     if tiled:
         a.q_cu, a.n_seq = _i32(q_cu_seqlens, "q_cu_seqlens"), int(n_seq)
         a.max_q_tiles = (int(max_row_tokens) + 15) // 16
-        _check(_lib("attention_talk").mf_talk_attention_tile(ctypes.addressof(a), 1 if paged else 0,
-                                                             _stream()), "talk_attention_tile",
-               2 if splits > 1 else 1)
-        return
+        code = _lib("attention_talk").mf_talk_attention_tile(ctypes.addressof(a), 1 if paged else 0,
+                                                             _stream())
+        if code != 2001:             # a grid the tiled kernel does not take goes to the kernel below
+            _check(code, "talk_attention_tile", 2 if splits > 1 else 1)
+            return
     _check(_lib("attention_talk").mf_talk_attention(ctypes.addressof(a), 1 if paged else 0,
                                                     dtype_code(q.dtype), _stream()),
            "talk_attention", 2 if splits > 1 else 1)
