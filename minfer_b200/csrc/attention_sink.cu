@@ -206,6 +206,7 @@ struct SinkArgs {
     float scale;
     const float* sink_logit;  // [n_heads] score of the sink, or nullptr for 0
     float softcap;            // > 0: s <- softcap * tanh(s / softcap) before the bias
+    int keep_first;           // > 0: keys at positions below it stay visible beyond the window
 };
 
 // tanh through one exponential: 1 - 2 / (exp(2y) + 1); exact at both ends (exp -> inf or 0)
@@ -257,7 +258,6 @@ __global__ void __launch_bounds__(SA_WARPS * 32) sink_attention_generic_kernel(S
     const int b = a.row_seq[row];
     const int pos = a.row_pos[row];
     const int lo = sink_first_key(pos, a.window, a.chunk);
-    const int hi = pos + 1;
     const float r1 = a.r1 ? a.r1[head] : 0.0f;
     const float r2 = a.r1 ? a.r2[head] : 0.0f;
     const float sink_score = (a.sink && a.sink_logit) ? a.sink_logit[head] : 0.0f;
@@ -277,7 +277,10 @@ __global__ void __launch_bounds__(SA_WARPS * 32) sink_attention_generic_kernel(S
 #pragma unroll
     for (int i = 0; i < NACC; ++i) acc[i] = 0.0f;
 
-    for (int j0 = lo; j0 < hi; j0 += 32) {
+    // two stretches of keys: the kept first ones the window no longer covers, then the window
+    const int kept_hi = min(a.keep_first, lo);
+    for (int seg = kept_hi > 0 ? 0 : 1; seg < 2; ++seg)
+    for (int j0 = seg == 0 ? 0 : lo, hi = seg == 0 ? kept_hi : pos + 1; j0 < hi; j0 += 32) {
         const int j = j0 + lane;
         const bool valid = j < hi;
         long long krow = 0;                           // index of key j's row: [..][hk][j]
@@ -340,7 +343,8 @@ static int sink_check(const SinkArgs& a, int dtype) {
     if (dtype != MF_DTYPE_F32 && dtype != MF_DTYPE_BF16) return MF_ERR_UNSUPPORTED;
     if (a.hd < 1 || a.hd > SA_GEN_MAX_D || a.vd < 1 || a.vd > SA_GEN_MAX_D) return MF_ERR_UNSUPPORTED;
     if (a.n_kv < 1 || a.n_heads % a.n_kv != 0) return MF_ERR_ARGUMENT;
-    if (a.window < 0 || a.chunk < 0 || a.softcap < 0.0f) return MF_ERR_ARGUMENT;
+    if (a.window < 0 || a.chunk < 0 || a.softcap < 0.0f || a.keep_first < 0) return MF_ERR_ARGUMENT;
+    if (a.keep_first > 0 && a.chunk > 0) return MF_ERR_UNSUPPORTED;
     return 0;
 }
 
@@ -369,13 +373,14 @@ static SinkArgs sink_args(const void* q, const void* k, const void* v, const int
                           const int* row_pos, const int* cu_seqlens, const int* page_table,
                           int table_stride, int ring, void* out, const float* r1, const float* r2,
                           int rows, int n_heads, int n_kv, int hd, int vd, int window, int chunk,
-                          int sink, float scale, const float* sink_logit, float softcap) {
+                          int sink, float scale, const float* sink_logit, float softcap,
+                          int keep_first = 0) {
     SinkArgs a;
     a.q = q; a.k = k; a.v = v; a.row_seq = row_seq; a.row_pos = row_pos; a.cu_seqlens = cu_seqlens;
     a.page_table = page_table; a.table_stride = table_stride; a.ring = ring; a.out = out;
     a.r1 = r1; a.r2 = r2; a.rows = rows; a.n_heads = n_heads; a.n_kv = n_kv; a.hd = hd; a.vd = vd;
     a.window = window; a.chunk = chunk; a.sink = sink ? 1 : 0; a.scale = scale;
-    a.sink_logit = sink_logit; a.softcap = softcap;
+    a.sink_logit = sink_logit; a.softcap = softcap; a.keep_first = keep_first;
     return a;
 }
 
@@ -386,10 +391,11 @@ extern "C" int mf_sink_attention_packed(const void* q, const void* k, const void
                                         const int* cu_seqlens, void* out, const float* r1,
                                         const float* r2, int rows, int n_heads, int n_kv, int hd,
                                         int vd, int window, int chunk, int sink, float scale,
-                                        const float* sink_logit, float softcap,
+                                        const float* sink_logit, float softcap, int keep_first,
                                         int dtype, cudaStream_t stream) {
     SinkArgs a = sink_args(q, k, v, row_seq, row_pos, cu_seqlens, nullptr, 0, 0, out, r1, r2, rows,
-                           n_heads, n_kv, hd, vd, window, chunk, sink, scale, sink_logit, softcap);
+                           n_heads, n_kv, hd, vd, window, chunk, sink, scale, sink_logit, softcap,
+                           keep_first);
     const int bad = sink_check(a, dtype);
     if (bad) return bad;
     return sink_generic_launch<false>(a, dtype, stream);
@@ -402,11 +408,12 @@ extern "C" int mf_sink_attention_paged(const void* q, const void* k_cache, const
                                        void* out, const float* r1, const float* r2, int rows,
                                        int n_heads, int n_kv, int hd, int vd, int window,
                                        int chunk, int sink, float scale,
-                                       const float* sink_logit, float softcap, int dtype,
-                                       cudaStream_t stream) {
+                                       const float* sink_logit, float softcap, int keep_first,
+                                       int dtype, cudaStream_t stream) {
     SinkArgs a = sink_args(q, k_cache, v_cache, row_seq, row_pos, nullptr, page_table,
                            table_stride, ring, out, r1, r2, rows, n_heads, n_kv, hd, vd, window,
-                           chunk, sink, scale, sink_logit, softcap);
+                           chunk, sink, scale, sink_logit, softcap, keep_first);
+    if (keep_first > 0 && ring > 0) return MF_ERR_ARGUMENT;       // a ring forgets the first keys
     const int bad = sink_check(a, dtype);
     if (bad) return bad;
     if (page_table == nullptr) return MF_ERR_ARGUMENT;

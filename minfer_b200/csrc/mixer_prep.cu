@@ -552,3 +552,132 @@ extern "C" int mf_head_linear(const HeadLinearArgs* args, int dtype, cudaStream_
     else return MF_ERR_UNSUPPORTED;
     return MF_LAUNCH_CHECK();
 }
+
+// ------------------------------------------------------------------------------------------
+// head_prepare: what qk_prepare does, head by head.  A warp owns one head of one token: a query
+// head, or a key head together with its value head.  Each query and key head is optionally
+// RMS-normed by itself (x / sqrt(mean(x^2) + eps) * weight, one weight of the head's width shared
+// by all heads), `rot_dims` dimensions from the head's start are rotated, and the result is
+// multiplied by q_mul / k_mul.  Outputs are bfloat16 or float32; a caller that keeps no cache and
+// reads its values from the projection passes null for the places it does not want.
+// ------------------------------------------------------------------------------------------
+struct HeadPrepArgs {
+    const float* proj;        // [tokens][in_width]
+    long long in_width;
+    const int* positions;
+    const int* token_row;
+    const int* seq_end;
+    const double* inv_freq;   // [rot_dims / 2] or null
+    const float* q_norm_w;    // [qw] or null
+    const float* k_norm_w;    // [kw] or null
+    void* q_out;              // [tokens][n_heads][qw]
+    void* k_out;              // [tokens][n_kv][kw] or null
+    void* v_out;              // [tokens][n_kv][vw] or null
+    void* k_cache;            // [pages][n_kv][64][kw] or null
+    void* v_cache;            // [pages][n_kv][64][vw] or null
+    const int* page_table;
+    int table_stride, ring;
+    int q_off, n_heads, qw, k_off, n_kv, kw, v_off, vw;
+    int rot_dims, rot_style;
+    float rot_mag, eps, q_mul, k_mul;
+    unsigned* status;
+};
+
+// the head at `seg` (width w) normed, rotated and scaled; element d goes to dst[d] and, if page_dst
+// is not null, to page_dst[d]
+template <typename T>
+__device__ __forceinline__ void head_prep_one(const float* seg, int w, const float* norm_w, float mul,
+                                              int pos, const HeadPrepArgs& a, T* dst, T* page_dst,
+                                              int lane) {
+    float rinv = 1.0f;
+    if (norm_w != nullptr) {
+        float ss = 0.0f;
+        for (int d = lane; d < w; d += 32) ss = fmaf(seg[d], seg[d], ss);
+        ss = warp_sum(ss);
+        rinv = 1.0f / sqrtf(ss / (float)w + a.eps);
+    }
+    const int half = a.rot_dims >> 1;
+    for (int d = lane; d < w; d += 32) {
+        float v = seg[d] * rinv;
+        if (norm_w != nullptr) v *= norm_w[d];
+        if (d < a.rot_dims) {
+            int pair, partner;
+            bool first;
+            if (a.rot_style == 0) { first = d < half; pair = first ? d : d - half; partner = first ? d + half : d - half; }
+            else { first = (d & 1) == 0; pair = d >> 1; partner = first ? d + 1 : d - 1; }
+            float other = seg[partner] * rinv;
+            if (norm_w != nullptr) other *= norm_w[partner];
+            double ang = (double)pos * a.inv_freq[pair];
+            ang -= 6.283185307179586476925286766559 * floor(ang * 0.15915494309189533576888376337251);
+            float s, c;
+            sincosf((float)ang, &s, &c);
+            c *= a.rot_mag; s *= a.rot_mag;
+            v = first ? v * c - other * s : v * c + other * s;
+        }
+        const T y = from_f32<T>(v * mul);
+        if (dst) dst[d] = y;
+        if (page_dst) page_dst[d] = y;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) head_prepare_kernel(HeadPrepArgs a, long long items) {
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= items) return;
+    const int per_token = a.n_heads + a.n_kv;
+    const int t = (int)(item / per_token);
+    const int h = (int)(item - (long long)t * per_token);
+    const int pos = a.positions[t];
+    pdl_wait();
+    const float* row = a.proj + (size_t)t * a.in_width;
+    if (h < a.n_heads) {
+        head_prep_one<T>(row + a.q_off + (size_t)h * a.qw, a.qw, a.q_norm_w, a.q_mul, pos, a,
+                         (T*)a.q_out + ((size_t)t * a.n_heads + h) * a.qw, (T*)nullptr, lane);
+        return;
+    }
+    const int hk = h - a.n_heads;
+    int page = -1;
+    if (a.k_cache != nullptr) {
+        const int b = a.token_row[t];
+        bool keep = true;
+        int p_eff = pos;
+        if (a.ring > 0) {
+            keep = pos >= a.seq_end[b] - a.ring;
+            p_eff = pos % a.ring;
+        }
+        if (keep) {
+            page = a.page_table[(size_t)b * a.table_stride + (p_eff >> 6)];
+            if (page < 0 && lane == 0) atomicOr(a.status, MF_STATUS_BAD_POSITION);
+        }
+    }
+    const int in_page = pos & (MF_PAGE - 1);
+    T* k_dst = a.k_out ? (T*)a.k_out + ((size_t)t * a.n_kv + hk) * a.kw : nullptr;
+    T* k_page = page >= 0 ? (T*)a.k_cache + (((size_t)page * a.n_kv + hk) * MF_PAGE + in_page) * a.kw : nullptr;
+    head_prep_one<T>(row + a.k_off + (size_t)hk * a.kw, a.kw, a.k_norm_w, a.k_mul, pos, a, k_dst, k_page, lane);
+    if (a.v_out == nullptr && (page < 0 || a.v_cache == nullptr)) return;
+    const float* vs = row + a.v_off + (size_t)hk * a.vw;
+    T* v_dst = a.v_out ? (T*)a.v_out + ((size_t)t * a.n_kv + hk) * a.vw : nullptr;
+    T* v_page = (page >= 0 && a.v_cache) ? (T*)a.v_cache + (((size_t)page * a.n_kv + hk) * MF_PAGE + in_page) * a.vw : nullptr;
+    for (int d = lane; d < a.vw; d += 32) {
+        const T y = from_f32<T>(vs[d]);
+        if (v_dst) v_dst[d] = y;
+        if (v_page) v_page[d] = y;
+    }
+}
+
+extern "C" int mf_head_prepare(const HeadPrepArgs* args, int n_tokens, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const HeadPrepArgs a = *args;
+    if (a.rot_dims < 0 || (a.rot_dims & 1) || (a.rot_dims > 0 && a.inv_freq == nullptr)) return MF_ERR_ARGUMENT;
+    if (a.rot_dims > a.qw || a.rot_dims > a.kw || a.n_heads < 1 || a.n_kv < 0) return MF_ERR_ARGUMENT;
+    if ((a.k_cache == nullptr) != (a.v_cache == nullptr)) return MF_ERR_ARGUMENT;
+    if (a.k_cache != nullptr && a.page_table == nullptr) return MF_ERR_ARGUMENT;
+    const long long items = (long long)n_tokens * (a.n_heads + a.n_kv);
+    dim3 grid((unsigned)((items + 7) / 8)), block(256);
+    if (dtype == MF_DTYPE_F32) mf_launch(head_prepare_kernel<float>, grid, block, 0, stream, a, items);
+    else if (dtype == MF_DTYPE_BF16) mf_launch(head_prepare_kernel<__nv_bfloat16>, grid, block, 0, stream, a, items);
+    else return MF_ERR_UNSUPPORTED;
+    return MF_LAUNCH_CHECK();
+}

@@ -1,6 +1,7 @@
 // Routed feed-forward (a mixture of small gated experts): the router's choice and the experts'
 // products for steps of few tokens.
 //
+//   moe_route_scored   the router that scores with a softmax over all outputs (see there)
 //   moe_route      per token: the `top` largest of its float32 router logits (ties: the lower
 //                  index), weights = softmax over the chosen logits only; a warp per token
 //   moe_up         hidden[t][k][f] = act(Wg_e x_t)[f] * (Wu_e x_t)[f] for token t's k-th expert e: a
@@ -12,6 +13,9 @@
 //                  products over its rows: count the pairs per expert, turn the counts into
 //                  offsets, give every pair its row (pairs of an expert keep their order), gather
 //                  the tokens' rows, and add the experts' weighted rows back into the residual
+// The act(..) of moe_up is silu (act 0) or the clamped form (act 2): g' sigmoid(alpha g') (u' + 1) with
+// g' = min(g, limit), u' = clamp(u, -limit, limit).  Choices e >= n_real name experts without
+// weights whose output is the token's input itself: moe_up skips them, moe_down adds w x_t.
 // Expert weights are stacked: gate and up [experts][ff][width] each or, rows alternating, as one
 // [experts][2 ff][width]; down [experts][width][ff].
 // Dot products accumulate in float32; `hidden` is in the activation type.
@@ -66,6 +70,66 @@ extern "C" int mf_moe_route(const float* logits, int* idx, float* wts, int n_tok
     return MF_LAUNCH_CHECK();
 }
 
+// The other way to route: scores = softmax over ALL router outputs; the `top` outputs with the
+// largest score + correction (ties: the lower index) are chosen; their weights are the scores
+// themselves (no correction, not renormalized).  `stride` floats separate the rows of `logits`
+// (a row may carry more columns than `experts`).  A warp per token.
+__global__ void __launch_bounds__(256)
+moe_route_scored_kernel(const float* __restrict__ logits, long long stride,
+                        const float* __restrict__ correction, int* __restrict__ idx,
+                        float* __restrict__ wts, int n_tokens, int experts, int top) {
+    pdl_prologue();
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= n_tokens) return;
+    const float* z = logits + (size_t)t * stride;
+    float zmax = -INFINITY;
+    for (int e = lane; e < experts; e += 32) zmax = fmaxf(zmax, z[e]);
+    zmax = warp_max(zmax);
+    float sum = 0.f;
+    for (int e = lane; e < experts; e += 32) sum += expf(z[e] - zmax);
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    int chosen_i[MOE_MAX_TOP];
+    float chosen_s[MOE_MAX_TOP];
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY, best_s = 0.f;
+        int best_i = 0x7fffffff;
+        for (int e = lane; e < experts; e += 32) {
+            bool taken = false;
+            for (int p = 0; p < k; ++p) taken |= chosen_i[p] == e;
+            const float s = expf(z[e] - zmax) * inv;
+            const float v = s + (correction ? correction[e] : 0.f);
+            if (!taken && (v > best || (v == best && e < best_i))) { best = v; best_i = e; best_s = s; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const float os = __shfl_xor_sync(0xffffffffu, best_s, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+            if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; best_s = os; }
+        }
+        chosen_i[k] = best_i;
+        chosen_s[k] = best_s;
+    }
+    if (lane == 0) {
+        for (int k = 0; k < top; ++k) {
+            idx[(size_t)t * top + k] = chosen_i[k];
+            wts[(size_t)t * top + k] = chosen_s[k];
+        }
+    }
+}
+
+extern "C" int mf_moe_route_scored(const float* logits, long long stride, const float* correction,
+                                   int* idx, float* wts, int n_tokens, int experts, int top,
+                                   cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (top < 1 || top > MOE_MAX_TOP || top > experts) return MF_ERR_UNSUPPORTED;
+    mf_launch(moe_route_scored_kernel, dim3((n_tokens + 7) / 8), dim3(256), 0, stream, logits, stride,
+              correction, idx, wts, n_tokens, experts, top);
+    return MF_LAUNCH_CHECK();
+}
+
 __device__ __forceinline__ float moe_dot(const float* w, const float* x, int n, int lane) {
     float s = 0.f;
     for (int i = lane; i < n; i += 32) s = fmaf(w[i], x[i], s);
@@ -95,7 +159,8 @@ template <typename TX, typename TW>
 __global__ void __launch_bounds__(256)
 moe_up_kernel(const TX* __restrict__ x, const TW* __restrict__ wg, const TW* __restrict__ wu,
               long long w_row, long long w_expert, const int* __restrict__ idx,
-              TX* __restrict__ hidden, int width, int ff, int top) {
+              TX* __restrict__ hidden, int width, int ff, int top, int n_real, int act, float limit,
+              float alpha) {
     pdl_launch_dependents();
     extern __shared__ float moe_x[];
     // pairs run along x, the fastest: the blocks of one tile of rows are placed together, so pairs
@@ -107,12 +172,21 @@ moe_up_kernel(const TX* __restrict__ x, const TW* __restrict__ wg, const TW* __r
     for (int i = threadIdx.x; i < width; i += blockDim.x) moe_x[i] = to_f32(x[(size_t)t * width + i]);
     const int e = idx[pair];
     __syncthreads();
+    if (e >= n_real) return;                       // an expert without weights: it hands its input on
     const int f_end = min(ff, (int)(blockIdx.y + 1) * MOE_ROWS);
     for (int f = blockIdx.y * MOE_ROWS + warp; f < f_end; f += n_warps) {
         const size_t wrow = (size_t)e * w_expert + (size_t)f * w_row;
         const float g = warp_sum(moe_dot(wg + wrow, moe_x, width, lane));
         const float u = warp_sum(moe_dot(wu + wrow, moe_x, width, lane));
-        if (lane == 0) hidden[(size_t)pair * ff + f] = from_f32<TX>(g / (1.0f + expf(-g)) * u);
+        if (lane == 0) {
+            float v;
+            if (act == 0) v = g / (1.0f + expf(-g)) * u;
+            else {
+                const float gc = fminf(g, limit), uc = fminf(fmaxf(u, -limit), limit);
+                v = gc / (1.0f + expf(-alpha * gc)) * (uc + 1.0f);
+            }
+            hidden[(size_t)pair * ff + f] = from_f32<TX>(v);
+        }
     }
 }
 
@@ -121,7 +195,8 @@ moe_up_kernel(const TX* __restrict__ x, const TW* __restrict__ wg, const TW* __r
 template <typename TX, typename TW>
 __global__ void __launch_bounds__(256)
 moe_down_kernel(const TX* __restrict__ hidden, const TW* __restrict__ wd, const int* __restrict__ idx,
-                const float* __restrict__ wts, float* __restrict__ h, int width, int ff, int top) {
+                const float* __restrict__ wts, float* __restrict__ h, int width, int ff, int top,
+                int n_real, const TX* __restrict__ x) {
     pdl_launch_dependents();
     extern __shared__ float moe_hid[];             // [top][ff]
     const int t = blockIdx.x;                      // tokens along x, as the pairs above
@@ -135,7 +210,8 @@ moe_down_kernel(const TX* __restrict__ hidden, const TW* __restrict__ wd, const 
         float sum = 0.f;
         for (int k = 0; k < top; ++k) {
             const int e = idx[(size_t)t * top + k];
-            const float d = warp_sum(moe_dot(wd + ((size_t)e * width + c) * ff, moe_hid + k * ff, ff, lane));
+            const float d = e >= n_real ? to_f32(x[(size_t)t * width + c])
+                : warp_sum(moe_dot(wd + ((size_t)e * width + c) * ff, moe_hid + k * ff, ff, lane));
             sum = fmaf(wts[(size_t)t * top + k], d, sum);
         }
         if (lane == 0) h[(size_t)t * width + c] += sum;
@@ -148,9 +224,9 @@ extern "C" int mf_moe_experts(const void* x, int x_dtype, const void* wg, const 
                               long long w_row, long long w_expert,
                               const void* wd, int w_dtype, const int* idx, const float* wts,
                               void* hidden, float* h, int n_tokens, int width, int ff, int top,
-                              cudaStream_t stream) {
+                              int n_real, int act, float limit, float alpha, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (top < 1 || top > MOE_MAX_TOP) return MF_ERR_UNSUPPORTED;
+    if (top < 1 || top > MOE_MAX_TOP || (act != 0 && act != 2)) return MF_ERR_UNSUPPORTED;
     const size_t smem_up = (size_t)width * sizeof(float), smem_dn = (size_t)top * ff * sizeof(float);
     if (smem_up > 48 * 1024 || smem_dn > 48 * 1024) return MF_ERR_UNSUPPORTED;
     if ((ff + MOE_ROWS - 1) / MOE_ROWS > 65535 || (width + MOE_COLS - 1) / MOE_COLS > 65535)
@@ -160,9 +236,10 @@ extern "C" int mf_moe_experts(const void* x, int x_dtype, const void* wg, const 
 #define MF_MOE(TX, TW) \
     do { \
         mf_launch(moe_up_kernel<TX, TW>, grid_up, dim3(256), smem_up, stream, (const TX*)x, \
-                  (const TW*)wg, (const TW*)wu, w_row, w_expert, idx, (TX*)hidden, width, ff, top); \
+                  (const TW*)wg, (const TW*)wu, w_row, w_expert, idx, (TX*)hidden, width, ff, top, n_real, \
+                  act, limit, alpha); \
         mf_launch(moe_down_kernel<TX, TW>, grid_dn, dim3(256), smem_dn, stream, (const TX*)hidden, \
-                  (const TW*)wd, idx, wts, h, width, ff, top); \
+                  (const TW*)wd, idx, wts, h, width, ff, top, n_real, (const TX*)x); \
     } while (0)
     if (x_dtype == MF_DTYPE_F32 && w_dtype == MF_DTYPE_F32) MF_MOE(float, float);
     else if (x_dtype == MF_DTYPE_BF16 && w_dtype == MF_DTYPE_BF16) MF_MOE(__nv_bfloat16, __nv_bfloat16);

@@ -1200,3 +1200,185 @@ extern "C" int mf_depth_mix(const float* hist, long long hist_stride, int n_hist
               hist_stride, n_hist, rows, last, w, out, n_rows, width);
     return MF_LAUNCH_CHECK();
 }
+
+// ------------------------------------------------------------------------------------
+// norm_add: h[t][:] += mult * y[t][:] / sqrt(mean(y[t]^2) + eps) * w[:], the residual add of a
+// layer that norms a sublayer's OUTPUT.  `y` may come as `n_partials` K splits [splits][rows][width]
+// (added here in split order, plus an optional bias) or as one float32 tensor (n_partials = 0).
+// A block per row; the row is read twice (it sits in L1 the second time).
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+norm_add_kernel(float* __restrict__ h, const float* __restrict__ y, int n_partials, long long split_stride,
+                const float* __restrict__ bias, const float* __restrict__ w, int width, float eps,
+                float mult) {
+    pdl_prologue();
+    __shared__ float scratch[33];
+    extern __shared__ float na_row[];
+    const size_t base = (size_t)blockIdx.x * width;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = y[base + i];
+        for (int s = 1; s < n_partials; ++s) v += y[(size_t)s * split_stride + base + i];
+        if (bias) v += bias[i];
+        na_row[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float f = mult / sqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) h[base + i] += na_row[i] * f * w[i];
+}
+
+extern "C" int mf_norm_add(float* h, const float* y, int n_partials, const float* bias, const float* w,
+                           int n_rows, int width, float eps, float mult, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (width < 1 || (size_t)width * sizeof(float) > 200 * 1024) return MF_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)width * sizeof(float);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(norm_add_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    mf_launch(norm_add_kernel, dim3(n_rows), dim3(256), smem, stream, h, y, n_partials,
+              (long long)n_rows * width, bias, w, width, eps, mult);
+    return MF_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// Activations on float32 products, written in the activation type.
+//   unary_act    kind 0: the erf form of gelu, 0.5 z (1 + erf(z / sqrt 2))
+//   gated_act    from rows [gate (ff) | up (ff)]: kind 0 silu(g) u; kind 1 gelu_tanh(g) u;
+//                kind 2 the clamped form g' sigmoid(alpha g') (u' + 1), g' = min(g, limit),
+//                u' = clamp(u, -limit, limit); optionally times sigmoid of one number per row
+//                (row_gate[t * row_gate_stride])
+//   gate_mul     o[t][c] <- o[t][c] * sigmoid(gate[t * gate_width + gate_off + c]) * mul, in place
+//   table_gate   out[t][d] = gelu_tanh(a[t][d]) * table[token(t)][off + d]: a per-token input
+//                looked up by token id (token(t) = ids[rows[t]] when the step kept only some rows)
+// ------------------------------------------------------------------------------------
+__device__ __forceinline__ float act_gelu_tanh(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename TO>
+__global__ void unary_act_kernel(const float* __restrict__ z, TO* __restrict__ out, long long n, int kind) {
+    pdl_prologue();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x) {
+        const float v = z[i];
+        out[i] = from_f32<TO>(0.5f * v * (1.0f + erff(v * 0.7071067811865476f)));
+    }
+}
+
+static inline dim3 mf_flat_grid(long long n) {
+    const long long cap_blocks = (long long)mf_sm_count() * 16;
+    const long long want = (n + 255) / 256;
+    return dim3((unsigned)(want < cap_blocks ? want : cap_blocks));
+}
+
+extern "C" int mf_unary_act(const float* z, void* out, int out_dtype, long long n, int kind,
+                            cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (kind != 0) return MF_ERR_ARGUMENT;
+    if (out_dtype == MF_DTYPE_F32)
+        mf_launch(unary_act_kernel<float>, mf_flat_grid(n), dim3(256), 0, stream, z, (float*)out, n, kind);
+    else if (out_dtype == MF_DTYPE_BF16)
+        mf_launch(unary_act_kernel<__nv_bfloat16>, mf_flat_grid(n), dim3(256), 0, stream, z,
+                  (__nv_bfloat16*)out, n, kind);
+    else return MF_ERR_UNSUPPORTED;
+    return MF_LAUNCH_CHECK();
+}
+
+template <typename TO>
+__global__ void gated_act_kernel(const float* __restrict__ gu, TO* __restrict__ out, long long total, int ff,
+                                 int kind, float limit, float alpha, const float* __restrict__ row_gate,
+                                 long long row_gate_stride) {
+    pdl_prologue();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / ff;
+        const int f = (int)(i - t * ff);
+        float g = gu[(size_t)t * 2 * ff + f], u = gu[(size_t)t * 2 * ff + ff + f];
+        float v;
+        if (kind == 0) v = g / (1.0f + expf(-g)) * u;
+        else if (kind == 1) v = act_gelu_tanh(g) * u;
+        else {
+            g = fminf(g, limit);
+            u = fminf(fmaxf(u, -limit), limit);
+            v = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+        }
+        if (row_gate) v *= 1.0f / (1.0f + expf(-row_gate[(size_t)t * row_gate_stride]));
+        out[i] = from_f32<TO>(v);
+    }
+}
+
+extern "C" int mf_gated_act(const float* gu, void* out, int out_dtype, int n_rows, int ff, int kind,
+                            float limit, float alpha, const float* row_gate, long long row_gate_stride,
+                            cudaStream_t stream) {
+    const long long total = (long long)n_rows * ff;
+    if (total <= 0) return 0;
+    if (kind < 0 || kind > 2) return MF_ERR_ARGUMENT;
+    if (out_dtype == MF_DTYPE_F32)
+        mf_launch(gated_act_kernel<float>, mf_flat_grid(total), dim3(256), 0, stream, gu, (float*)out,
+                  total, ff, kind, limit, alpha, row_gate, row_gate_stride);
+    else if (out_dtype == MF_DTYPE_BF16)
+        mf_launch(gated_act_kernel<__nv_bfloat16>, mf_flat_grid(total), dim3(256), 0, stream, gu,
+                  (__nv_bfloat16*)out, total, ff, kind, limit, alpha, row_gate, row_gate_stride);
+    else return MF_ERR_UNSUPPORTED;
+    return MF_LAUNCH_CHECK();
+}
+
+template <typename T>
+__global__ void gate_mul_kernel(T* __restrict__ o, const float* __restrict__ gate, long long gate_width,
+                                int gate_off, long long total, int width, float mul) {
+    pdl_prologue();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / width;
+        const int c = (int)(i - t * width);
+        const float z = gate[(size_t)t * gate_width + gate_off + c];
+        o[i] = from_f32<T>(to_f32(o[i]) * (mul / (1.0f + expf(-z))));
+    }
+}
+
+extern "C" int mf_gate_mul(void* o, int dtype, const float* gate, long long gate_width, int gate_off,
+                           int n_rows, int width, float mul, cudaStream_t stream) {
+    const long long total = (long long)n_rows * width;
+    if (total <= 0) return 0;
+    if (dtype == MF_DTYPE_F32)
+        mf_launch(gate_mul_kernel<float>, mf_flat_grid(total), dim3(256), 0, stream, (float*)o, gate,
+                  gate_width, gate_off, total, width, mul);
+    else if (dtype == MF_DTYPE_BF16)
+        mf_launch(gate_mul_kernel<__nv_bfloat16>, mf_flat_grid(total), dim3(256), 0, stream,
+                  (__nv_bfloat16*)o, gate, gate_width, gate_off, total, width, mul);
+    else return MF_ERR_UNSUPPORTED;
+    return MF_LAUNCH_CHECK();
+}
+
+template <typename TT, typename TO>
+__global__ void table_gate_kernel(const float* __restrict__ a, const TT* __restrict__ table, long long table_width,
+                                  int off, const int* __restrict__ ids, const int* __restrict__ rows,
+                                  TO* __restrict__ out, long long total, int dim, int vocab,
+                                  unsigned* __restrict__ status) {
+    pdl_prologue();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / dim;
+        const int d = (int)(i - t * dim);
+        int id = ids[rows ? rows[t] : t];
+        if (id < 0 || id >= vocab) { atomicOr(status, MF_STATUS_BAD_TOKEN); id = 0; }
+        out[i] = from_f32<TO>(act_gelu_tanh(a[i]) * to_f32(table[(size_t)id * table_width + off + d]));
+    }
+}
+
+extern "C" int mf_table_gate(const float* a, const void* table, int table_dtype, long long table_width,
+                             int off, const int* ids, const int* rows, void* out, int out_dtype,
+                             int n_rows, int dim, int vocab, unsigned* status, cudaStream_t stream) {
+    const long long total = (long long)n_rows * dim;
+    if (total <= 0) return 0;
+#define MF_TG(TT, TO) \
+    mf_launch(table_gate_kernel<TT, TO>, mf_flat_grid(total), dim3(256), 0, stream, a, (const TT*)table, \
+              table_width, off, ids, rows, (TO*)out, total, dim, vocab, status)
+    if (table_dtype == MF_DTYPE_F32 && out_dtype == MF_DTYPE_F32) MF_TG(float, float);
+    else if (table_dtype == MF_DTYPE_BF16 && out_dtype == MF_DTYPE_BF16) MF_TG(__nv_bfloat16, __nv_bfloat16);
+    else if (table_dtype == MF_DTYPE_F32 && out_dtype == MF_DTYPE_BF16) MF_TG(float, __nv_bfloat16);
+    else if (table_dtype == MF_DTYPE_BF16 && out_dtype == MF_DTYPE_F32) MF_TG(__nv_bfloat16, float);
+    else return MF_ERR_UNSUPPORTED;
+#undef MF_TG
+    return MF_LAUNCH_CHECK();
+}

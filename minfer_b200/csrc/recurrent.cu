@@ -598,3 +598,143 @@ extern "C" int mf_gated_group_norm(const float* y, const float* proj, long long 
                   z_off, w, (__nv_bfloat16*)out, inner, groups, eps);
     return MF_LAUNCH_CHECK();
 }
+
+// ------------------------------------------------------------------------------------------
+// selective_scan: the recurrence of the first Mamba form, a state of n_state numbers per CHANNEL
+// with a decay of its own per (channel, state):
+//     dt = softplus(dt_raw[t][c]);  S[c][n] <- exp(dt * A[c][n]) S[c][n] + dt u[t][c] B[t][n],
+//     A = -exp(A_log);  y = sum_n S[c][n] C[t][n] + D[c] u[t][c];  out = y * silu(z[t][c]) * mul
+// A block owns SL_CH channels of one row; SL_NS threads share a channel and keep its states
+// (n = lane + SL_NS * i) and decays' rates in registers; tokens are staged SL_TC at a time.
+// The state is float32 [slots][channels][n_state] and takes the row's last state.
+// ------------------------------------------------------------------------------------------
+#define SL_NS 8
+#define SL_CH 32
+#define SL_TC 16
+#define SL_MAX_N 256
+
+struct SelectiveArgs {
+    const float* u;          // [tokens][channels]
+    const float* dt_raw;     // [tokens][channels]
+    const float* bc;         // B at bc[t * bc_width + b_off + n], C at bc[t * bc_width + c_off + n]
+    long long bc_width;
+    int b_off, c_off;
+    const float* z;          // z[t * z_width + z_off + c]
+    long long z_width;
+    int z_off;
+    const float* a_log;      // [channels][n_state]
+    const float* d_skip;     // [channels]
+    float* state;            // [slots][channels][n_state]
+    const int* cu_seqlens;
+    const int* slots;
+    void* out;               // [tokens][channels]
+    int n_rows, channels, n_state;
+    float mul;
+};
+
+__device__ __forceinline__ float sl_softplus(float x) {
+    return log1pf(expf(-fabsf(x))) + fmaxf(x, 0.0f);
+}
+
+template <typename TO, int NREG>
+__global__ void __launch_bounds__(SL_CH * SL_NS) selective_scan_kernel(SelectiveArgs a) {
+    pdl_launch_dependents();
+    extern __shared__ float sl_smem[];
+    const int N = a.n_state, C = a.channels;
+    float* b_s = sl_smem;                       // [SL_TC][N]
+    float* c_s = b_s + SL_TC * N;               // [SL_TC][N]
+    float* dt_s = c_s + SL_TC * N;              // [SL_TC][SL_CH]
+    float* u_s = dt_s + SL_TC * SL_CH;          // [SL_TC][SL_CH]
+    const int b = blockIdx.y;
+    const int l = threadIdx.x % SL_NS, cc = threadIdx.x / SL_NS;
+    const int ch = blockIdx.x * SL_CH + cc;
+    const bool live = ch < C;
+    const int t0 = a.cu_seqlens[b], t1 = a.cu_seqlens[b + 1];
+    const int slot = a.slots[b];
+    float A[NREG], S[NREG];
+#pragma unroll
+    for (int i = 0; i < NREG; ++i) {
+        const int n = l + SL_NS * i;
+        A[i] = (live && n < N) ? -expf(a.a_log[(size_t)ch * N + n]) : 0.0f;
+    }
+    const float dsk = live ? a.d_skip[ch] : 0.0f;
+    pdl_wait();
+    float* st = a.state + ((size_t)slot * C + (live ? ch : 0)) * N;
+#pragma unroll
+    for (int i = 0; i < NREG; ++i) {
+        const int n = l + SL_NS * i;
+        S[i] = (live && n < N) ? st[n] : 0.0f;
+    }
+    for (int tc = t0; tc < t1; tc += SL_TC) {
+        const int n_here = min(SL_TC, t1 - tc);
+        __syncthreads();
+        for (int i = threadIdx.x; i < n_here * N; i += blockDim.x) {
+            const int tt = i / N, n = i - tt * N;
+            const float* row = a.bc + (size_t)(tc + tt) * a.bc_width;
+            b_s[i] = row[a.b_off + n];
+            c_s[i] = row[a.c_off + n];
+        }
+        for (int i = threadIdx.x; i < n_here * SL_CH; i += blockDim.x) {
+            const int tt = i / SL_CH, c2 = i - tt * SL_CH;
+            const int chn = blockIdx.x * SL_CH + c2;
+            float dt = 0.0f, uu = 0.0f;
+            if (chn < C) {
+                dt = sl_softplus(a.dt_raw[(size_t)(tc + tt) * C + chn]);
+                uu = a.u[(size_t)(tc + tt) * C + chn];
+            }
+            dt_s[i] = dt;
+            u_s[i] = uu;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < n_here; ++tt) {
+            const float dt = dt_s[tt * SL_CH + cc], uu = u_s[tt * SL_CH + cc];
+            const float du = dt * uu;
+            const float* br = b_s + tt * N;
+            const float* cr = c_s + tt * N;
+            float acc = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NREG; ++i) {
+                const int n = l + SL_NS * i;
+                if (n < N) {
+                    S[i] = fmaf(expf(dt * A[i]), S[i], du * br[n]);
+                    acc = fmaf(S[i], cr[n], acc);
+                }
+            }
+#pragma unroll
+            for (int o = SL_NS / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (l == 0 && live) {
+                const float y = fmaf(dsk, uu, acc);
+                const float zz = a.z[(size_t)(tc + tt) * a.z_width + a.z_off + ch];
+                ((TO*)a.out)[(size_t)(tc + tt) * C + ch] = from_f32<TO>(y * zz / (1.0f + expf(-zz)) * a.mul);
+            }
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < NREG; ++i) {
+            const int n = l + SL_NS * i;
+            if (n < N) st[n] = S[i];
+        }
+    }
+}
+
+extern "C" int mf_selective_scan(const SelectiveArgs* args, int out_dtype, cudaStream_t stream) {
+    const SelectiveArgs a = *args;
+    if (a.n_rows <= 0) return 0;
+    if (a.n_state < 1 || a.n_state > SL_MAX_N || a.channels < 1 || a.n_rows > 65535) return MF_ERR_UNSUPPORTED;
+    dim3 grid((a.channels + SL_CH - 1) / SL_CH, a.n_rows), block(SL_CH * SL_NS);
+    const size_t smem = (size_t)(2 * SL_TC * a.n_state + 2 * SL_TC * SL_CH) * sizeof(float);
+    const int nreg = (a.n_state + SL_NS - 1) / SL_NS;
+#define MF_SL2(TO, N) mf_launch(selective_scan_kernel<TO, N>, grid, block, smem, stream, a)
+#define MF_SL(TO) \
+    do { \
+        if (nreg <= 1) MF_SL2(TO, 1); else if (nreg <= 2) MF_SL2(TO, 2); else if (nreg <= 4) MF_SL2(TO, 4); \
+        else if (nreg <= 8) MF_SL2(TO, 8); else if (nreg <= 16) MF_SL2(TO, 16); else MF_SL2(TO, 32); \
+    } while (0)
+    if (out_dtype == MF_DTYPE_F32) MF_SL(float);
+    else if (out_dtype == MF_DTYPE_BF16) MF_SL(__nv_bfloat16);
+    else return MF_ERR_UNSUPPORTED;
+#undef MF_SL
+#undef MF_SL2
+    return MF_LAUNCH_CHECK();
+}

@@ -541,6 +541,7 @@ class Engine:
                                          device=self.device)
                     K.gather_rows(h, want_rows, picked)
                     h = picked
+                    ctx.extras["kept_rows"] = want_rows      # row r of h is token kept_rows[r] now
             # the norm that reads h after this block's feed-forward: the next block's first, if
             # it can take its input prepared, or the model's last (the head applies the scale)
             if depth is not None:

@@ -117,6 +117,15 @@ def _sig_ops(lib: ctypes.CDLL) -> None:
     lib.mf_poly_norm.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
     lib.mf_depth_mix.argtypes = [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_int, c_int, c_void_p]
+    lib.mf_norm_add.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float,
+                                c_float, c_void_p]
+    lib.mf_unary_act.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p]
+    lib.mf_gated_act.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float,
+                                 c_void_p, c_longlong, c_void_p]
+    lib.mf_gate_mul.argtypes = [c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_float,
+                                c_void_p]
+    lib.mf_table_gate.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p,
+                                  c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
 
 
 def _sig_gemm_simt(lib: ctypes.CDLL) -> None:
@@ -136,9 +145,10 @@ def _sig_attention_sink(lib: ctypes.CDLL) -> None:
     lib.mf_unit_norm_kvstore.argtypes = ([c_void_p, c_int] + [c_void_p] * 9 + [c_int] * 7 +
                                          [c_float, c_int, c_int, c_void_p, c_void_p])
     lib.mf_sink_attention_packed.argtypes = ([c_void_p] * 9 + [c_int] * 8 +
-                                             [c_float, c_void_p, c_float, c_int, c_void_p])
+                                             [c_float, c_void_p, c_float, c_int, c_int, c_void_p])
     lib.mf_sink_attention_paged.argtypes = ([c_void_p] * 6 + [c_int, c_int] + [c_void_p] * 3 +
-                                            [c_int] * 8 + [c_float, c_void_p, c_float, c_int, c_void_p])
+                                            [c_int] * 8 + [c_float, c_void_p, c_float, c_int, c_int,
+                                                           c_void_p])
 
 
     lib.mf_sink_attention_mma_supported.argtypes = [c_int, c_int]
@@ -204,11 +214,19 @@ def _sig_recurrent(lib: ctypes.CDLL) -> None:
                                 [c_int] * 6 + [c_void_p])
     lib.mf_gated_group_norm.argtypes = [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_void_p,
                                         c_int, c_int, c_int, c_int, c_float, c_void_p]
+    lib.mf_selective_scan.argtypes = [c_void_p, c_int, c_void_p]
+
+
+def _sig_retention(lib: ctypes.CDLL) -> None:
+    lib.mf_retention_scan.argtypes = [c_void_p, c_void_p]
+    lib.mf_unit_norm_gate.argtypes = [c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int,
+                                      c_int, c_int, c_float, c_int, c_float, c_void_p]
 
 
 def _sig_mixer_prep(lib: ctypes.CDLL) -> None:
     lib.mf_qk_prepare.argtypes = [c_void_p, c_int, c_int, c_void_p]
     lib.mf_head_linear.argtypes = [c_void_p, c_int, c_void_p]
+    lib.mf_head_prepare.argtypes = [c_void_p, c_int, c_int, c_void_p]
 
 
 def _sig_delta_rule(lib: ctypes.CDLL) -> None:
@@ -231,9 +249,12 @@ def _sig_attention_talk(lib: ctypes.CDLL) -> None:
 
 def _sig_moe(lib: ctypes.CDLL) -> None:
     lib.mf_moe_route.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    lib.mf_moe_route_scored.argtypes = [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
+                                        c_int, c_int, c_void_p]
     lib.mf_moe_experts.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_longlong,
                                    c_void_p, c_int, c_void_p,
-                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                   c_int, c_int, c_float, c_float, c_void_p]
     lib.mf_moe_counts.argtypes = [c_void_p, c_void_p, c_int, c_void_p]
     lib.mf_moe_place.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                  c_void_p]
@@ -242,7 +263,7 @@ def _sig_moe(lib: ctypes.CDLL) -> None:
                                    c_void_p]
 
 
-_SIGNATURES = {"delta_rule": _sig_delta_rule, "attention_talk": _sig_attention_talk, "moe": _sig_moe,
+_SIGNATURES = {"retention": _sig_retention, "delta_rule": _sig_delta_rule, "attention_talk": _sig_attention_talk, "moe": _sig_moe,
                "attention_prefill_tc": _sig_attention_prefill_tc, "recurrent": _sig_recurrent,
                "mixer_prep": _sig_mixer_prep,
                "attention_sink": _sig_attention_sink,
@@ -1184,9 +1205,33 @@ def moe_route(logits: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, top: i
                                     experts, int(top), _stream()), "moe_route")
 
 
+EXPERT_ACTIVATIONS = {"silu": 0, "clamped_swish": 2}
+
+
+def moe_route_scored(logits: torch.Tensor, correction: Optional[torch.Tensor], idx: torch.Tensor,
+                     wts: torch.Tensor, top: int, outputs: int) -> None:
+    """Per row of ``logits`` (float32 [tokens, >= outputs]; only the first ``outputs`` columns are
+    the router's): scores = softmax over the outputs; the ``top`` largest of score + correction
+    (ties: the lower index) into ``idx``, and their scores (uncorrected, not renormalized) into
+    ``wts``."""
+    n = logits.shape[0]
+    if (idx.shape != (n, top) or wts.shape != (n, top) or logits.shape[1] < outputs
+            or logits.stride(1) != 1 or (correction is not None and correction.numel() != outputs)):
+        raise KernelError("moe_route_scored: shapes do not fit")
+    if not logits.is_cuda or logits.dtype != torch.float32:
+        raise KernelError("moe_route_scored: logits must be float32 on a CUDA device")
+    _check(_lib("moe").mf_moe_route_scored(
+        logits.data_ptr(), logits.stride(0), _f32(correction, "correction"), _i32(idx, "idx"),
+        _f32(wts, "wts"), n, int(outputs), int(top), _stream()), "moe_route_scored")
+
+
 def moe_experts(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
-                idx: torch.Tensor, wts: torch.Tensor, hidden: torch.Tensor, h: torch.Tensor) -> None:
-    """h[t] += sum_k wts[t][k] Wd_e (silu(Wg_e x_t) * (Wu_e x_t)), e = idx[t][k].  ``w_gate`` and
+                idx: torch.Tensor, wts: torch.Tensor, hidden: torch.Tensor, h: torch.Tensor,
+                activation: str = "silu", limit: float = 0.0, alpha: float = 1.0) -> None:
+    """h[t] += sum_k wts[t][k] Wd_e (silu(Wg_e x_t) * (Wu_e x_t)), e = idx[t][k]; with
+    ``activation`` "clamped_swish" an expert's hidden values are g' sigmoid(alpha g') (u' + 1),
+    g' = min(g, limit), u' = clamp(u, -limit, limit).  A choice e >= the number of stacked experts
+    names an expert without weights that returns the token's input: h[t] += wts[t][k] x_t.  ``w_gate`` and
     ``w_up`` [experts, ff, width] are two stacks or strided views of one stack with alternating
     rows (equal strides, rows contiguous); ``w_down`` [experts, width, ff]; ``hidden``
     [tokens, top, ff] in the type of ``x`` is scratch; ``h`` float32.  For steps of few tokens (a
@@ -1204,7 +1249,8 @@ def moe_experts(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_dow
     _check(_lib("moe").mf_moe_experts(
         _ptr(x, "x"), dtype_code(x.dtype), w_gate.data_ptr(), w_up.data_ptr(), w_gate.stride(1),
         w_gate.stride(0), _ptr(w_down, "w_down"), dtype_code(w_gate.dtype), _i32(idx, "idx"),
-        _f32(wts, "wts"), _ptr(hidden, "hidden"), _f32(h, "h"), n, width, ff, top, _stream()),
+        _f32(wts, "wts"), _ptr(hidden, "hidden"), _f32(h, "h"), n, width, ff, top, int(experts),
+        EXPERT_ACTIVATIONS[activation], float(limit), float(alpha), _stream()),
         "moe_experts", 2)
 
 
@@ -1243,6 +1289,224 @@ def moe_combine(y: torch.Tensor, where: torch.Tensor, wts: torch.Tensor, h: torc
         raise KernelError("moe_combine: shapes do not fit")
     _check(_lib("moe").mf_moe_combine(_f32(y, "y"), _i32(where, "where"), _f32(wts, "wts"),
                                       _f32(h, "h"), n, y.shape[1], top, _stream()), "moe_combine")
+
+
+
+# ---------------------------------------------------------------------------------------
+# layers that norm a sublayer's output; activations on float32 products (csrc/ops.cu)
+# ---------------------------------------------------------------------------------------
+def norm_add(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, mult: float,
+             bias: Optional[torch.Tensor] = None) -> None:
+    """h[t] += mult * y[t] / sqrt(mean(y[t]^2) + eps) * weight.  ``y`` float32 [rows, width], or the
+    K splits of a product [splits, rows, width] that are added here in split order (plus ``bias``)."""
+    n, width = h.shape
+    splits = 0
+    if y.dim() == 3:
+        splits = y.shape[0]
+        if y.shape[1:] != (n, width):
+            raise KernelError("norm_add: the partial sums do not fit the stream")
+    elif y.shape != (n, width):
+        raise KernelError("norm_add: shapes do not fit")
+    if weight.numel() != width:
+        raise KernelError("norm_add: the weight has another width")
+    _check(_lib("ops").mf_norm_add(_f32(h, "h"), _f32(y, "y"), splits, _f32(bias, "bias"),
+                                   _f32(weight, "weight"), n, width, float(eps), float(mult),
+                                   _stream()), "norm_add")
+
+
+UNARY_ACTIVATIONS = {"gelu": 0}
+GATED_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}
+
+
+def unary_act(z: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+    """out = act(z), z float32; "gelu" is the erf form 0.5 z (1 + erf(z / sqrt 2))."""
+    if out.shape != z.shape:
+        raise KernelError("unary_act: shapes do not fit")
+    _check(_lib("ops").mf_unary_act(_f32(z, "z"), _ptr(out, "out"), dtype_code(out.dtype), z.numel(),
+                                    UNARY_ACTIVATIONS[activation], _stream()), "unary_act")
+
+
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str, limit: float = 0.0,
+              alpha: float = 1.0, row_gate: Optional[torch.Tensor] = None) -> None:
+    """From float32 rows [gate (ff) | up (ff)]: silu(g) u, gelu_tanh(g) u, or ("clamped_swish")
+    g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit); times
+    sigmoid(row_gate[t]) if ``row_gate`` (float32, one number a row, any row stride) is given."""
+    n, ff = out.shape
+    if gate_up.shape != (n, 2 * ff):
+        raise KernelError("gated_act: shapes do not fit")
+    rg, rg_stride = None, 0
+    if row_gate is not None:
+        if row_gate.dtype != torch.float32 or not row_gate.is_cuda or row_gate.shape[0] != n:
+            raise KernelError("gated_act: the row gate must be float32 on the device, one a row")
+        rg, rg_stride = row_gate.data_ptr(), row_gate.stride(0)
+    _check(_lib("ops").mf_gated_act(_f32(gate_up, "gate_up"), _ptr(out, "out"), dtype_code(out.dtype),
+                                    n, ff, GATED_ACTIVATIONS[activation], float(limit), float(alpha),
+                                    rg, rg_stride, _stream()), "gated_act")
+
+
+def gate_mul(o: torch.Tensor, gate: torch.Tensor, gate_off: int, mul: float = 1.0) -> None:
+    """o[t][c] <- o[t][c] * sigmoid(gate[t][gate_off + c]) * mul, in place; ``gate`` float32 rows."""
+    n, width = o.shape
+    if gate.shape[0] != n or gate_off + width > gate.shape[1]:
+        raise KernelError("gate_mul: shapes do not fit")
+    _check(_lib("ops").mf_gate_mul(_ptr(o, "o"), dtype_code(o.dtype), _f32(gate, "gate"),
+                                   gate.shape[1], int(gate_off), n, width, float(mul), _stream()),
+           "gate_mul")
+
+
+def table_gate(a: torch.Tensor, table: torch.Tensor, off: int, ids: torch.Tensor,
+               rows: Optional[torch.Tensor], out: torch.Tensor, status: torch.Tensor) -> None:
+    """out[t][d] = gelu_tanh(a[t][d]) * table[ids[rows[t] if rows else t]][off + d]."""
+    n, dim = a.shape
+    if out.shape != (n, dim) or off + dim > table.shape[1] or (rows is not None and rows.numel() != n):
+        raise KernelError("table_gate: shapes do not fit")
+    _check(_lib("ops").mf_table_gate(_f32(a, "a"), _ptr(table, "table"), dtype_code(table.dtype),
+                                     table.shape[1], int(off), _i32(ids, "ids"), _i32(rows, "rows"),
+                                     _ptr(out, "out"), dtype_code(out.dtype), n, dim, table.shape[0],
+                                     _i32(status, "status"), _stream()), "table_gate")
+
+
+# ---------------------------------------------------------------------------------------
+# heads prepared one by one (csrc/mixer_prep.cu)
+# ---------------------------------------------------------------------------------------
+class _HeadPrepArgs(ctypes.Structure):
+    _fields_ = ([("proj", c_void_p), ("in_width", c_longlong)] +
+                [(n, c_void_p) for n in ("positions", "token_row", "seq_end", "inv_freq", "q_norm_w",
+                                         "k_norm_w", "q_out", "k_out", "v_out", "k_cache", "v_cache",
+                                         "page_table")] +
+                [(n, c_int) for n in ("table_stride", "ring", "q_off", "n_heads", "qw", "k_off", "n_kv",
+                                      "kw", "v_off", "vw", "rot_dims", "rot_style")] +
+                [(n, c_float) for n in ("rot_mag", "eps", "q_mul", "k_mul")] + [("status", c_void_p)])
+
+
+def head_prepare(proj: torch.Tensor, positions: torch.Tensor, token_row: torch.Tensor,
+                 seq_end: torch.Tensor, q_out: torch.Tensor, k_out: Optional[torch.Tensor],
+                 v_out: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                 v_cache: Optional[torch.Tensor], page_table: Optional[torch.Tensor],
+                 table_stride: int, ring: int, *, q_off: int, n_heads: int, q_width: int, k_off: int,
+                 n_kv: int, k_width: int, v_off: int, v_width: int,
+                 q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float,
+                 inv_freq: Optional[torch.Tensor], rot_dims: int, rot_style: int,
+                 rot_magnitude: float, q_mul: float, k_mul: float, status: torch.Tensor) -> None:
+    """From the float32 projection rows: every query head (``n_heads`` of ``q_width`` at column
+    ``q_off``) and key head (``n_kv`` of ``k_width`` at ``k_off``) RMS-normed BY ITSELF with a weight
+    of the head's width shared by all heads (None: no norm), its first ``rot_dims`` dimensions
+    rotated, the result times ``q_mul`` / ``k_mul``; values (``n_kv`` heads of ``v_width`` at
+    ``v_off``) copied.  Writes q, the step's k and v and the cache's pages (each optional except q),
+    in the type of ``q_out``."""
+    n = proj.shape[0]
+    dt = q_out.dtype
+    for t in (k_out, v_out, k_cache, v_cache):
+        if t is not None and t.dtype != dt:
+            raise KernelError("head_prepare: q, k, v and the cache must share one dtype")
+    if q_out.numel() != n * n_heads * q_width:
+        raise KernelError("head_prepare: q has the wrong size")
+    if k_cache is not None and (k_cache.shape[-1] != k_width or k_cache.shape[1] != n_kv
+                                or v_cache is None or v_cache.shape[-1] != v_width):
+        raise KernelError("head_prepare: the cache has other key or value widths")
+    wants_v = v_out is not None or v_cache is not None
+    need = max(q_off + n_heads * q_width, k_off + n_kv * k_width,
+               v_off + n_kv * v_width if wants_v else 0)
+    if proj.dim() != 2 or proj.shape[1] < need:
+        raise KernelError("head_prepare: the projection is narrower than its segments")
+    for w, width in ((q_norm, q_width), (k_norm, k_width)):
+        if w is not None and w.numel() != width:
+            raise KernelError("head_prepare: a norm weight has another width than its heads")
+    a = _HeadPrepArgs()
+    a.proj, a.in_width = _f32(proj, "proj"), proj.shape[1]
+    a.positions, a.token_row = _i32(positions, "positions"), _i32(token_row, "token_row")
+    a.seq_end, a.inv_freq = _i32(seq_end, "seq_end"), _f64(inv_freq, "inv_freq")
+    a.q_norm_w, a.k_norm_w = _f32(q_norm, "q_norm"), _f32(k_norm, "k_norm")
+    a.q_out, a.k_out, a.v_out = _ptr(q_out, "q_out"), _ptr(k_out, "k_out"), _ptr(v_out, "v_out")
+    a.k_cache, a.v_cache = _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache")
+    a.page_table, a.table_stride, a.ring = _i32(page_table, "page_table"), int(table_stride), int(ring)
+    a.q_off, a.n_heads, a.qw = int(q_off), int(n_heads), int(q_width)
+    a.k_off, a.n_kv, a.kw = int(k_off), int(n_kv), int(k_width)
+    a.v_off, a.vw = int(v_off), int(v_width)
+    a.rot_dims, a.rot_style = int(rot_dims), int(rot_style)
+    a.rot_mag, a.eps, a.q_mul, a.k_mul = float(rot_magnitude), float(eps), float(q_mul), float(k_mul)
+    a.status = _i32(status, "status")
+    _check(_lib("mixer_prep").mf_head_prepare(ctypes.addressof(a), n, dtype_code(dt), _stream()),
+           "head_prepare")
+
+
+# ---------------------------------------------------------------------------------------
+# retention and the selective scan (csrc/retention.cu, csrc/recurrent.cu)
+# ---------------------------------------------------------------------------------------
+class _RetentionArgs(ctypes.Structure):
+    _fields_ = [("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("v_width", c_longlong),
+                ("v_off", c_int), ("decay", c_void_p), ("state", c_void_p), ("cu_seqlens", c_void_p),
+                ("slots", c_void_p), ("out", c_void_p), ("n_rows", c_int), ("heads", c_int),
+                ("D", c_int), ("Dv", c_int)]
+
+
+def retention_scan(q: torch.Tensor, k: torch.Tensor, proj: torch.Tensor, v_off: int,
+                   decay: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor,
+                   slots: torch.Tensor, out: torch.Tensor, n_rows: int) -> None:
+    """Per (row, head), tokens one after another: S <- decay[h] S + k v^T; out = S^T q.  ``q``, ``k``
+    float32 [tokens, heads, D] (prepared); v the columns v_off .. of ``proj`` (float32 rows, heads of
+    Dv); S float32 in ``state`` [slots, heads, Dv, D]; ``out`` float32 [tokens, heads * Dv]."""
+    n, heads, d = q.shape
+    dv = state.shape[2]
+    if (k.shape != q.shape or state.shape[1:] != (heads, dv, d) or out.shape != (n, heads * dv)
+            or proj.shape[0] != n or v_off + heads * dv > proj.shape[1] or decay.numel() != heads):
+        raise KernelError("retention_scan: shapes do not fit")
+    a = _RetentionArgs()
+    a.q, a.k, a.v = _f32(q, "q"), _f32(k, "k"), _f32(proj, "proj")
+    a.v_width, a.v_off = proj.shape[1], int(v_off)
+    a.decay, a.state = _f32(decay, "decay"), _f32(state, "state")
+    a.cu_seqlens, a.slots = _i32(cu_seqlens, "cu_seqlens"), _i32(slots, "slots")
+    a.out, a.n_rows, a.heads, a.D, a.Dv = _f32(out, "out"), int(n_rows), heads, d, dv
+    _check(_lib("retention").mf_retention_scan(ctypes.addressof(a), _stream()), "retention_scan")
+
+
+def unit_norm_gate(o: torch.Tensor, gate: torch.Tensor, gate_off: int, out: torch.Tensor,
+                   heads: int, eps: float, activation: str = "silu", mul: float = 1.0) -> None:
+    """Each head of ``o`` (float32 [tokens, heads * Dv]) divided by its root mean square (eps inside
+    the root, no weight), times silu or sigmoid of the gate (columns gate_off .. of float32 rows),
+    times ``mul``."""
+    n = o.shape[0]
+    dv = o.shape[1] // heads
+    if out.shape != o.shape or gate.shape[0] != n or gate_off + heads * dv > gate.shape[1]:
+        raise KernelError("unit_norm_gate: shapes do not fit")
+    _check(_lib("retention").mf_unit_norm_gate(
+        _f32(o, "o"), _f32(gate, "gate"), gate.shape[1], int(gate_off), _ptr(out, "out"),
+        dtype_code(out.dtype), n, heads, dv, float(eps), HEAD_GATES[activation], float(mul),
+        _stream()), "unit_norm_gate")
+
+
+class _SelectiveArgs(ctypes.Structure):
+    _fields_ = [("u", c_void_p), ("dt_raw", c_void_p), ("bc", c_void_p), ("bc_width", c_longlong),
+                ("b_off", c_int), ("c_off", c_int), ("z", c_void_p), ("z_width", c_longlong),
+                ("z_off", c_int), ("a_log", c_void_p), ("d_skip", c_void_p), ("state", c_void_p),
+                ("cu_seqlens", c_void_p), ("slots", c_void_p), ("out", c_void_p), ("n_rows", c_int),
+                ("channels", c_int), ("n_state", c_int), ("mul", c_float)]
+
+
+def selective_scan(u: torch.Tensor, dt_raw: torch.Tensor, bc: torch.Tensor, b_off: int, c_off: int,
+                   z: torch.Tensor, z_off: int, a_log: torch.Tensor, d_skip: torch.Tensor,
+                   state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor,
+                   out: torch.Tensor, n_rows: int, mul: float = 1.0) -> None:
+    """Per (row, channel c), tokens one after another: dt = softplus(dt_raw[t][c]);
+    S[c][n] <- exp(-exp(a_log[c][n]) dt) S[c][n] + dt u[t][c] B[t][n]; y = sum_n S[c][n] C[t][n] +
+    d_skip[c] u[t][c]; out = y silu(z[t][z_off + c]) mul.  B and C are columns of ``bc``; everything
+    float32 but ``out``; S in ``state`` [slots, channels, n_state]."""
+    n, channels = u.shape
+    n_state = a_log.shape[1]
+    if (dt_raw.shape != u.shape or out.shape != u.shape or a_log.shape[0] != channels
+            or state.shape[1:] != (channels, n_state) or d_skip.numel() != channels
+            or bc.shape[0] != n or max(b_off, c_off) + n_state > bc.shape[1]
+            or z.shape[0] != n or z_off + channels > z.shape[1]):
+        raise KernelError("selective_scan: shapes do not fit")
+    a = _SelectiveArgs()
+    a.u, a.dt_raw, a.bc = _f32(u, "u"), _f32(dt_raw, "dt_raw"), _f32(bc, "bc")
+    a.bc_width, a.b_off, a.c_off = bc.shape[1], int(b_off), int(c_off)
+    a.z, a.z_width, a.z_off = _f32(z, "z"), z.shape[1], int(z_off)
+    a.a_log, a.d_skip, a.state = _f32(a_log, "a_log"), _f32(d_skip, "d_skip"), _f32(state, "state")
+    a.cu_seqlens, a.slots = _i32(cu_seqlens, "cu_seqlens"), _i32(slots, "slots")
+    a.out, a.n_rows, a.channels, a.n_state, a.mul = _ptr(out, "out"), int(n_rows), channels, n_state, float(mul)
+    _check(_lib("recurrent").mf_selective_scan(ctypes.addressof(a), dtype_code(out.dtype), _stream()),
+           "selective_scan")
 
 
 # ---------------------------------------------------------------------------------------
@@ -1290,11 +1554,12 @@ def sink_attention_packed(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, row
                           r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], n_heads: int,
                           n_kv: int, head_dim: int, value_dim: int, window: int, chunk: int,
                           sink: bool, scale: float, sink_logit: Optional[torch.Tensor] = None,
-                          softcap: float = 0.0) -> None:
+                          softcap: float = 0.0, keep_first: int = 0) -> None:
     """Attention of the step's own packed keys and values (whole prompts): scores
     (q . k) * scale - r1 ln(1 + r2 (i - j)), causal, optional window and chunk mask, a sink
     of score 0 in the softmax if ``sink`` (of score ``sink_logit[h]`` if given), the scores
-    soft-capped first (cap * tanh(s / cap)) if ``softcap`` > 0."""
+    soft-capped first (cap * tanh(s / cap)) if ``softcap`` > 0; with ``keep_first`` the keys at
+    positions below it stay visible however far the window has moved on."""
     rows = q.shape[0]
     if out.shape != (rows, n_heads * value_dim) or (r1 is None) != (r2 is None):
         raise KernelError("sink_attention_packed: shapes do not fit")
@@ -1302,8 +1567,8 @@ def sink_attention_packed(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, row
         _ptr(q, "q"), _ptr(k, "k"), _ptr(v, "v"), _i32(row_seq, "row_seq"), _i32(row_pos, "row_pos"),
         _i32(cu_seqlens, "cu_seqlens"), _ptr(out, "out"), _f32(r1, "r1"), _f32(r2, "r2"), rows,
         n_heads, n_kv, head_dim, value_dim, int(window), int(chunk), 1 if sink else 0, float(scale),
-        _f32(sink_logit, "sink_logit"), float(softcap), dtype_code(q.dtype), _stream()),
-        "sink_attention_packed")
+        _f32(sink_logit, "sink_logit"), float(softcap), int(keep_first), dtype_code(q.dtype),
+        _stream()), "sink_attention_packed")
 
 
 def sink_attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -1312,7 +1577,7 @@ def sink_attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                          r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], n_heads: int,
                          n_kv: int, head_dim: int, value_dim: int, window: int, chunk: int,
                          sink: bool, scale: float, sink_logit: Optional[torch.Tensor] = None,
-                         softcap: float = 0.0) -> None:
+                         softcap: float = 0.0, keep_first: int = 0) -> None:
     """The same over the paged cache: every row of ``q`` is a query at its own position."""
     rows = q.shape[0]
     if out.shape != (rows, n_heads * value_dim) or (r1 is None) != (r2 is None):
@@ -1322,7 +1587,7 @@ def sink_attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
         _i32(row_pos, "row_pos"), _i32(page_table, "page_table"), int(table_stride), int(ring),
         _ptr(out, "out"), _f32(r1, "r1"), _f32(r2, "r2"), rows, n_heads, n_kv, head_dim, value_dim,
         int(window), int(chunk), 1 if sink else 0, float(scale), _f32(sink_logit, "sink_logit"),
-        float(softcap), dtype_code(q.dtype), _stream()), "sink_attention_paged")
+        float(softcap), int(keep_first), dtype_code(q.dtype), _stream()), "sink_attention_paged")
 
 
 def sink_attention_mma_supported(dtype: torch.dtype, head_dim: int, value_dim: int) -> bool:

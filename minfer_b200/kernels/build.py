@@ -42,6 +42,7 @@ LIBRARIES = {
     "delta_rule": ("delta_rule.cu", []),
     "attention_talk": ("attention_talk.cu", []),
     "moe": ("moe.cu", []),
+    "retention": ("retention.cu", []),
 }
 
 

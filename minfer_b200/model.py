@@ -69,11 +69,18 @@ class Model:
                                     Init(0.0, 0.02)))
         if p.head_bias_name is not None:
             specs.append(TensorSpec(p.head_bias_name, (p.vocab_size,), VECTOR, Init(0.0, 0.02)))
-        names = [s.name for s in specs]
-        if len(set(names)) != len(names):
-            dup = sorted({n for n in names if names.count(n) > 1})
-            raise ValueError(f"two parts ask for the same tensor: {', '.join(dup)}")
-        return specs
+        # several parts may share one tensor of the model (a table every layer reads a slice of):
+        # they ask for it in the same words, and it is listed once
+        seen: Dict[str, TensorSpec] = {}
+        unique = []
+        for s in specs:
+            first = seen.get(s.name)
+            if first is None:
+                seen[s.name] = s
+                unique.append(s)
+            elif (first.shape, first.role) != (s.shape, s.role):
+                raise ValueError(f"two parts ask for the tensor {s.name} in different forms")
+        return unique
 
     def model_parts(self) -> List[Any]:
         """The plan's parts around the blocks that this model has."""

@@ -12,7 +12,7 @@ from typing import Any, Dict, List, Mapping, Optional, Sequence
 import torch
 
 from ..config.base import LayerSpec
-from .base import Block, CallBinding, StateRequest, StepContext, settle_pending
+from .base import Block, CallBinding, Part, StateRequest, StepContext, settle_pending
 
 
 class PreNormBlock(Block):
@@ -111,3 +111,137 @@ class PreNormBlock(Block):
         # the feed-forward's last product may prepare the input of the norm that reads h next
         # (the next block's first, or the model's last), which the engine names
         self._call(self.feed_forward, x, scale, ctx, ctx.extras.get("next_norm"), h)
+
+
+class TokenSide(Part):
+    """A per-layer input looked up by token id, added to the stream after the feed-forward:
+
+        e = table[token][offset : offset + dim];   y = Wp (gelu_tanh(Wa x) * e)
+        x += mult * y / sqrt(mean(y^2) + eps) * w
+
+    ``table`` ([vocab, layers * dim]) is one tensor of the whole model, named without the layer's
+    prefix and shared by every layer's part; ``Wa`` [dim, width], ``Wp`` [width, dim] and the norm
+    weight ``w`` are the layer's own."""
+
+    capturable = True      # launches kernels only; safe inside a CUDA graph capture
+
+    def libraries(self, dtype: torch.dtype) -> List[str]:
+        return ["ops", "gemm_simt"] + (["gemm_tc"] if dtype == torch.bfloat16 else [])
+
+    def __init__(self, hidden_size: int, vocab_size: int, dim: int, offset: int, table_width: int,
+                 eps: float, mult: float = 1.0, table_name: str = "side.embed",
+                 gate_name: str = "side.gate", proj_name: str = "side.proj",
+                 norm_name: str = "side.norm", init_std: float = 0.02):
+        from .linear import Linear  # noqa: F401  (the products below)
+        if dim < 1 or offset < 0 or offset + dim > table_width:
+            raise ValueError(f"columns [{offset}, {offset + dim}) do not lie within a table of {table_width}")
+        self.hidden_size, self.vocab_size = int(hidden_size), int(vocab_size)
+        self.dim, self.offset, self.table_width = int(dim), int(offset), int(table_width)
+        self.eps, self.mult = float(eps), float(mult)
+        self.table_name, self.gate_name = table_name, gate_name
+        self.proj_name, self.norm_name = proj_name, norm_name
+        self.init_std = float(init_std)
+        self.table = self.gate = self.proj = self.norm = None
+
+    def tensor_specs(self, prefix: str) -> List:
+        from ..weights.spec import MATRIX, VECTOR, Init, TensorSpec
+        init = Init(0.0, self.init_std)
+        return [TensorSpec(self.table_name, (self.vocab_size, self.table_width), MATRIX, init),
+                TensorSpec(f"{prefix}{self.gate_name}", (self.dim, self.hidden_size), MATRIX, init),
+                TensorSpec(f"{prefix}{self.proj_name}", (self.hidden_size, self.dim), MATRIX, init),
+                TensorSpec(f"{prefix}{self.norm_name}", (self.hidden_size,), VECTOR, Init(1.0, 0.0))]
+
+    def load(self, prefix: str, weights: Dict[str, torch.Tensor]) -> None:
+        from .linear import Linear
+        self.table = weights[self.table_name]
+        self.gate = Linear(weights[f"{prefix}{self.gate_name}"])
+        self.proj = Linear(weights[f"{prefix}{self.proj_name}"])
+        self.norm = weights[f"{prefix}{self.norm_name}"]
+
+    def export(self, prefix: str) -> Dict[str, torch.Tensor]:
+        return {self.table_name: self.table, f"{prefix}{self.gate_name}": self.gate.weight,
+                f"{prefix}{self.proj_name}": self.proj.weight, f"{prefix}{self.norm_name}": self.norm}
+
+    def add(self, h: torch.Tensor, x: torch.Tensor, ctx: StepContext) -> None:
+        """``x``: the stream ``h`` in the activation type; the rows are the step's tokens or, after
+        the engine dropped rows, those that ``ctx.extras["kept_rows"]`` names."""
+        from ..kernels import api as K
+        n = h.shape[0]
+        a = self.gate.forward(x, torch.float32)
+        g = torch.empty((n, self.dim), dtype=ctx.act_dtype, device=h.device)
+        K.table_gate(a, self.table, self.offset, ctx.token_ids, ctx.extras.get("kept_rows"), g, ctx.status)
+        y = self.proj.forward(g, torch.float32)
+        K.norm_add(h, y, self.norm, self.eps, self.mult)
+
+
+class OutputNormBlock(Block):
+    """A block whose norms sit on the sublayers' OUTPUTS, the sublayers reading the stream itself:
+
+        h += mult * norm1(mixer(h));   h += mult * norm2(ffn(h))   (the second half optional)
+
+    followed, with ``side`` (the parameters of ``TokenSide``), by that part's per-token input."""
+
+    capturable = True      # launches kernels only; safe inside a CUDA graph capture
+    accepts_pending = False
+
+    def __init__(self, layer: LayerSpec, mult: float = 1.0, side: Optional[Mapping[str, Any]] = None):
+        from ..registry import build_part
+        self.prefix = layer.prefix
+        self.mult = float(mult)
+        self.mixer_norm = build_part("norm", layer.mixer_norm)
+        self.mixer = build_part("mixer", layer.mixer)
+        self.feed_forward_norm = self.feed_forward = None
+        if layer.feed_forward is not None:
+            self.feed_forward_norm = build_part("norm", layer.feed_forward_norm)
+            self.feed_forward = build_part("feed_forward", layer.feed_forward)
+        for norm in (self.mixer_norm, self.feed_forward_norm):
+            if norm is not None and norm.foldable() is None:
+                raise ValueError("this block adds y / rms(y) * w itself: its norms must be RMS norms")
+        self.side = TokenSide(mult=self.mult, **side) if side is not None else None
+
+    def parts(self):
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm,
+                                 self.feed_forward, self.side) if p is not None)
+
+    tensor_specs = PreNormBlock.tensor_specs
+    load = PreNormBlock.load
+    export = PreNormBlock.export
+
+    def libraries(self, dtype: torch.dtype) -> List[str]:
+        return ["ops"]
+
+    def _input(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        """The stream as the sublayers' products take it."""
+        if ctx.act_dtype == torch.float32:
+            return h
+        from ..kernels import api as K
+        x = torch.empty(h.shape, dtype=ctx.act_dtype, device=h.device)
+        K.cast(h, x)
+        return x
+
+    def _add_normed(self, h: torch.Tensor, y: torch.Tensor, norm, ctx: StepContext) -> None:
+        """h += mult * norm(y + whatever the sublayer's last product left pending)."""
+        from ..kernels import api as K
+        weight, eps, _ = norm.foldable()
+        pending = ctx.extras.pop("pending", None)
+        if pending is not None:
+            pending.settle(y)
+        K.norm_add(h, y, weight, eps, self.mult)
+
+    def mix(self, h: torch.Tensor, ctx: StepContext, binding: CallBinding) -> None:
+        ctx.extras.pop("prepared", None)
+        ctx.extras.pop("prepare_for", None)
+        ctx.input_scale = None
+        y = torch.zeros_like(h)
+        self.mixer.forward_add(self._input(h, ctx), ctx, binding, y)
+        self._add_normed(h, y, self.mixer_norm, ctx)
+
+    def feed(self, h: torch.Tensor, ctx: StepContext) -> None:
+        ctx.extras.pop("prepared", None)
+        ctx.extras.pop("prepare_for", None)
+        if self.feed_forward is not None:
+            y = torch.zeros_like(h)
+            self.feed_forward.forward_add(self._input(h, ctx), ctx, y)
+            self._add_normed(h, y, self.feed_forward_norm, ctx)
+        if self.side is not None:
+            self.side.add(h, self._input(h, ctx), ctx)

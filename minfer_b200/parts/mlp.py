@@ -127,12 +127,15 @@ class DenseMlp(FeedForward):
                  powers element by element, N(u) = u / sqrt(mean(u^2) + eps) over a token's
                  feed-forward values (``norm_eps``), in float32 on the product's float32 sums.
 
+    ``"gelu"``   the erf form 0.5 z (1 + erf(z / sqrt 2)), no learned numbers (and no tensor
+                 ``act_name``), in float32 on the product's float32 sums.
+
     Tensor names are parameters (``up_name``, ``down_name``, ``act_name``, each behind the
     layer's prefix)."""
 
     capturable = True      # launches kernels only; safe inside a CUDA graph capture
-    ACTIVATIONS = ("xielu", "poly_norm")
-    ACT_NUMBERS = {"xielu": 2, "poly_norm": 4}
+    ACTIVATIONS = ("xielu", "poly_norm", "gelu")
+    ACT_NUMBERS = {"xielu": 2, "poly_norm": 4, "gelu": 0}
 
     def libraries(self, dtype: torch.dtype) -> List[str]:
         return ["ops", "gemm_tc"] if dtype == torch.bfloat16 else ["ops", "gemm_simt"]
@@ -155,17 +158,20 @@ class DenseMlp(FeedForward):
 
     def tensor_specs(self, prefix: str) -> List[TensorSpec]:
         init = Init(0.0, self.init_std)
-        return [TensorSpec(f"{prefix}{self.up_name}", (self.intermediate_size, self.hidden_size),
-                           MATRIX, init),
-                TensorSpec(f"{prefix}{self.down_name}", (self.hidden_size, self.intermediate_size),
-                           MATRIX, init),
-                TensorSpec(f"{prefix}{self.act_name}", (self.ACT_NUMBERS[self.activation],), VECTOR,
-                           Init(0.0, 0.5))]
+        specs = [TensorSpec(f"{prefix}{self.up_name}", (self.intermediate_size, self.hidden_size),
+                            MATRIX, init),
+                 TensorSpec(f"{prefix}{self.down_name}", (self.hidden_size, self.intermediate_size),
+                            MATRIX, init)]
+        if self.ACT_NUMBERS[self.activation]:
+            specs.append(TensorSpec(f"{prefix}{self.act_name}", (self.ACT_NUMBERS[self.activation],),
+                                    VECTOR, Init(0.0, 0.5)))
+        return specs
 
     def load(self, prefix: str, weights: Dict[str, torch.Tensor]) -> None:
         self.up = Linear(weights[f"{prefix}{self.up_name}"])
         self.down = Linear(weights[f"{prefix}{self.down_name}"])
-        self.act_params = weights[f"{prefix}{self.act_name}"]
+        self.act_params = (weights[f"{prefix}{self.act_name}"] if self.ACT_NUMBERS[self.activation]
+                           else None)
         self.accepts_row_scale = self.up.takes_row_scale()
         if self.activation != "xielu":
             return
@@ -175,8 +181,10 @@ class DenseMlp(FeedForward):
         self._act_p, self._act_n = float(sp[0]), 0.5 + float(sp[1])
 
     def export(self, prefix: str) -> Dict[str, torch.Tensor]:
-        return {f"{prefix}{self.up_name}": self.up.weight, f"{prefix}{self.down_name}": self.down.weight,
-                f"{prefix}{self.act_name}": self.act_params}
+        out = {f"{prefix}{self.up_name}": self.up.weight, f"{prefix}{self.down_name}": self.down.weight}
+        if self.act_params is not None:
+            out[f"{prefix}{self.act_name}"] = self.act_params
+        return out
 
     def forward_add(self, x: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
         from ..kernels import gemm
@@ -186,6 +194,9 @@ class DenseMlp(FeedForward):
             # its own on the product's float32 rows
             z = self.up.forward(x, torch.float32, row_scale=ctx.input_scale)
             K.poly_norm(z, self.act_params, act, self.norm_eps)
+        elif self.activation == "gelu":
+            z = self.up.forward(x, torch.float32, row_scale=ctx.input_scale)
+            K.unary_act(z, act, "gelu")
         elif (x.shape[0] > 0 and self.up.takes_row_scale() and x.dtype == torch.bfloat16
                 and K.gemm_tc_supported(x, self.up.weight) and FUSE_ACTIVATION):
             # the activation rides on the up projection's epilogue

@@ -63,9 +63,12 @@ class ScoreSpec:
     r2: Optional[torch.Tensor] = None
     sink_logit: Optional[torch.Tensor] = None
     softcap: float = 0.0
+    keep_first: int = 0       # > 0: keys at positions below it stay visible beyond the window
 
     def reach(self) -> int:
         """Positions a query may look back, itself included (0: no bound)."""
+        if self.keep_first > 0:
+            return 0
         bounds = [b for b in (self.chunk, self.window) if b > 0]
         return min(bounds) if bounds else 0
 
@@ -82,7 +85,9 @@ def scored_attention(spec: ScoreSpec, q: torch.Tensor, k_step: Optional[torch.Te
     own_kv = ctx.from_start
     r1, r2 = spec.r1, spec.r2
     cap, sl = spec.softcap, spec.sink_logit
-    tensor_cores = K.sink_attention_mma_supported(act, hd, vd) and not FORCE_GENERIC
+    keep = spec.keep_first if spec.window > 0 else 0
+    tensor_cores = (K.sink_attention_mma_supported(act, hd, vd) and not FORCE_GENERIC
+                    and keep == 0)         # kept first tokens: the generic kernels
     # prompts: the tcgen05 kernel where keys and values have one size it takes, else mma.sync
     tcgen05 = (tensor_cores and PROMPT_KERNEL != "mma" and spec.scale > 0.0
                and K.sink_attention_tc_supported(act, hd, vd))
@@ -99,7 +104,8 @@ def scored_attention(spec: ScoreSpec, q: torch.Tensor, k_step: Optional[torch.Te
     if own_kv:
         K.sink_attention_packed(q, k_step, v_step, ctx.token_row, ctx.positions, ctx.cu_seqlens, o,
                                 r1, r2, nh, nk, hd, vd, spec.window, spec.chunk, spec.sink,
-                                spec.scale, sink_logit=spec.sink_logit, softcap=spec.softcap)
+                                spec.scale, sink_logit=spec.sink_logit, softcap=spec.softcap,
+                                keep_first=keep)
         return
     reach = spec.reach()
     if cache.ring and ctx.max_row_tokens > cache.ring - reach + 1:
@@ -130,7 +136,7 @@ def scored_attention(spec: ScoreSpec, q: torch.Tensor, k_step: Optional[torch.Te
     K.sink_attention_paged(q, cache.k, cache.v, ctx.token_row, ctx.positions, cache.page_table,
                            cache.table_stride, cache.ring, o, r1, r2, nh, nk, hd, vd, spec.window,
                            spec.chunk, spec.sink, spec.scale, sink_logit=spec.sink_logit,
-                           softcap=spec.softcap)
+                           softcap=spec.softcap, keep_first=keep)
 
 
 def project_out(out: Linear, o: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
