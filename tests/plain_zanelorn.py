@@ -102,6 +102,21 @@ def visible(T: int, window: int, first: int) -> torch.Tensor:
     return (j <= i) & ((i - j < window) | (j < first))
 
 
+def masked_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, window: int,
+                     first: int) -> torch.Tensor:
+    """q [T, H, D], k [T, G, D], v [T, G, Dv] of one sequence -> [T, H, Dv]."""
+    T, H = q.shape[0], q.shape[1]
+    G = k.shape[1]
+    see = visible(T, window, first)
+    out = torch.zeros(T, H, v.shape[2], dtype=q.dtype)
+    for h in range(H):
+        kv = h // (H // G)
+        s = (q[:, h] @ k[:, kv].T) * scale
+        s = s.masked_fill(~see, float("-inf"))
+        out[:, h] = torch.softmax(s, dim=-1) @ v[:, kv]
+    return out
+
+
 def windowed_attention(x: torch.Tensor, w: Mapping[str, torch.Tensor], p: str, m: Mapping,
                        eps: float) -> torch.Tensor:
     T = x.shape[0]
@@ -117,13 +132,7 @@ def windowed_attention(x: torch.Tensor, w: Mapping[str, torch.Tensor], p: str, m
     q = rotate_half(q, rot["dims"], rot["base"], divide)
     k = rotate_half(k, rot["dims"], rot["base"], divide)
     mask = m.get("mask") or {}
-    see = visible(T, mask.get("size", T + 1), mask.get("keep_first", 0))
-    out = torch.zeros(T, H, Dv, dtype=x.dtype)
-    for h in range(H):
-        kv = h // (H // G)
-        s = (q[:, h] @ k[:, kv].T) * m["scale"]
-        s = s.masked_fill(~see, float("-inf"))
-        out[:, h] = torch.softmax(s, dim=-1) @ v[:, kv]
+    out = masked_attention(q, k, v, m["scale"], mask.get("size", T + 1), mask.get("keep_first", 0))
     gate = torch.sigmoid(x @ w[p + "g"].T)
     return (out.reshape(T, H * Dv) * gate) @ w[p + "o"].T
 
@@ -169,14 +178,20 @@ def clamped_expert(x: torch.Tensor, w: Mapping[str, torch.Tensor], p: str, limit
 
 def route(x: torch.Tensor, w: Mapping[str, torch.Tensor], p: str, top: int):
     """(chosen [T, top], their weights [T, top], the margin between the last chosen and the first
-    left out, per token)."""
+    left out as a fraction of their scores, per token)."""
     s = torch.softmax(x @ w[p + "router"].T, dim=-1)
     pick = s + w[p + "correction"]
     order = torch.argsort(pick, dim=-1, descending=True, stable=True)
     chosen = order[:, :top]
     ranked = torch.gather(pick, 1, order)
-    margin = (ranked[:, top - 1] - ranked[:, top]) if ranked.shape[1] > top else torch.full(
-        (x.shape[0],), float("inf"), dtype=x.dtype)
+    if ranked.shape[1] > top:
+        # relative to the two scores it separates: rounding moves a score by a fraction of itself
+        near = torch.gather(s, 1, order[:, top - 1:top + 1]).sum(dim=-1) / 2
+        margin = (ranked[:, top - 1] - ranked[:, top]) / near.clamp(min=1e-30)
+        # two experts whose scores are next to nothing may change places without a trace
+        margin = torch.where(near < 0.005, torch.full_like(margin, float("inf")), margin)
+    else:
+        margin = torch.full((x.shape[0],), float("inf"), dtype=x.dtype)
     return chosen, torch.gather(s, 1, chosen), margin
 
 
@@ -234,6 +249,51 @@ def forward(cfg: Mapping, w: Mapping[str, torch.Tensor], tokens, streams: Option
         if streams is not None:
             streams.append(x.clone())
     return rms_norm(x, w["final.norm"], eps) @ w["head"].T
+
+
+def forward_sure(cfg: Mapping, w: Mapping[str, torch.Tensor], tokens, least_margin: float) -> torch.Tensor:
+    """``forward`` with NaN in the rows of every token for which some router's choice hangs on less
+    than ``least_margin``: an implementation that rounds its activations may choose otherwise there,
+    rightly, so a comparison leaves those rows out."""
+    margins: List[torch.Tensor] = []
+    logits = forward(cfg, w, tokens, None, margins).clone()
+    for m in margins:
+        logits[m < least_margin] = float("nan")
+    return logits
+
+
+def forward_marked(cfg: Mapping, w: Mapping[str, torch.Tensor], tokens, least_margin: float):
+    """(logits, sure): ``sure[t]`` is False where some router's choice at token t is a close call."""
+    margins: List[torch.Tensor] = []
+    logits = forward(cfg, w, tokens, None, margins)
+    sure = torch.ones(logits.shape[0], dtype=torch.bool)
+    for m in margins:
+        sure &= m >= least_margin
+    return logits, sure
+
+
+def generate_greedy(cfg: Mapping, w: Mapping[str, torch.Tensor], prompt: List[int], n_new: int) -> List[int]:
+    ids, out = list(prompt), []
+    for _ in range(n_new):
+        tok = int(torch.argmax(forward(cfg, w, ids)[-1]))
+        out.append(tok)
+        ids.append(tok)
+    return out
+
+
+def load_folder(folder: str, dtype: torch.dtype = torch.float64):
+    """(config.json as a dict, every tensor of model.safetensors in ``dtype``)."""
+    import json
+    import os
+    from safetensors import safe_open
+    with open(os.path.join(folder, "config.json")) as f:
+        cfg = json.load(f)
+    weights = {}
+    with safe_open(os.path.join(folder, "model.safetensors"), framework="pt") as f:
+        for name in f.keys():
+            t = f.get_tensor(name)
+            weights[name] = t.to(dtype) if t.is_floating_point() else t
+    return cfg, weights
 
 
 def load_weights(model, dtype=torch.float64) -> Dict[str, torch.Tensor]:

@@ -1,0 +1,444 @@
+"""Zanelorn through the engine against the plain implementation, in float32 and bfloat16: whole
+prompts and the stream after every layer; the last tokens one by one; every token a step from the
+first; prompts in portions down to two tokens; batches of unequal requests against each alone, one
+batch after another so that slots, pages and state are used again; a mixed step; decoding far past
+a window and a ring; models of one kind of layer and of sizes that are 1; greedy generation through
+the generator, the command line and the trace replay."""
+import copy
+import json
+import os
+import subprocess
+import sys
+import tempfile
+
+import numpy as np
+import pytest
+import torch
+
+import plain_zanelorn as P
+from helpers import logits_err, random_ids
+from zanelorn_cases import ZAN_A, ZAN_B, ZAN_C, make_folder
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = [37, 5, 131, 64, 1, 65, 11]
+# a router's choice that hangs on less than this fraction of the scores it separates is left out of
+# a comparison: rounding the activations to bfloat16 moves a score by about a hundredth of itself
+LEAST_MARGIN = {"float32": 1e-4, "bfloat16": 0.05}
+
+
+@pytest.fixture(scope="module", params=["A", "B", "C", "D"])
+def case(request):
+    folder = make_folder(request.param)
+    cfg, w = P.load_folder(folder)
+    prompts = [random_ids(n, cfg["vocab"], 900 + i) for i, n in enumerate(LENGTHS)]
+    plain = {dt: [Plain(*P.forward_marked(cfg, w, ids, m)) for ids in prompts]
+             for dt, m in LEAST_MARGIN.items()}
+    return {"name": request.param, "folder": folder, "cfg": cfg, "w": w, "prompts": prompts,
+            "plain": plain}
+
+
+def _engine(folder, dtype, max_tokens=4096, **kw):
+    from minfer_b200.engine.step import Engine
+    from minfer_b200.model import Model
+    return Engine(Model.from_folder(folder, dtype, "cuda:0"), max_tokens=max_tokens, **kw)
+
+
+class Plain:
+    """The plain logits of a sequence's positions and, for each, whether every router's choice
+    there is clear of a close call."""
+
+    def __init__(self, logits, sure):
+        self.logits, self.sure = logits, sure
+        self.shape = logits.shape
+
+    def __getitem__(self, idx):
+        return Plain(self.logits[idx], self.sure[idx])
+
+    @staticmethod
+    def cat(parts):
+        return Plain(torch.cat([p.logits for p in parts]), torch.cat([p.sure for p in parts]))
+
+
+def _plain(cfg, w, ids, dtype):
+    return Plain(*P.forward_marked(cfg, w, ids, LEAST_MARGIN[dtype]))
+
+
+def _close(got, want, dtype):
+    """Row by row, in the order of the positions.  A router's close call may rightly go the other
+    way in an engine that rounds otherwise; the token's logits then differ, and so do those of every
+    later token (its keys, values and state go on in the mixers of later layers).  So: a row must be
+    within the bound, unless it is a close call or comes after one that went the other way (shown by
+    that row itself being out of bound), where the comparison of the sequence ends.
+
+    bfloat16: this design divides every sublayer's output (and every retention head's, over as few as
+    8 numbers) by its root mean square, so a token whose output nearly cancels has its rounding
+    errors scaled up: a few rows in a hundred lie above the bound that holds for the others, none by
+    more than a factor of 8.  A fault of the cache, the state or the batch moves every later row by
+    tens of per cent and still fails."""
+    g = got.detach().to(torch.float64).cpu()
+    w = want.logits
+    top = max(1e-30, float(w.abs().max()))
+    if dtype == "float32":
+        err, bound, worst, few = (g - w).abs().max(dim=-1).values / top, 2e-5, 2e-5, 0.0
+    else:
+        from helpers import ROW_RMS_TOL
+        err, bound = (g - w).pow(2).mean(dim=-1).sqrt() / top, ROW_RMS_TOL
+        worst, few = 8 * bound, 0.05
+    checked, above = 0, 0
+    for t in range(w.shape[0]):
+        e = float(err[t])
+        if e >= bound:
+            if not bool(want.sure[t]):
+                break
+            assert e < worst, (t, e, worst)
+            above += 1
+        checked += 1
+    assert above <= max(1, int(few * checked)) if few else above == 0, (above, checked)
+    if w.shape[0] >= 20:
+        assert checked >= min(60, 0.25 * w.shape[0]), (checked, w.shape[0])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole_prompts_and_every_layer(case, dtype):
+    eng = _engine(case["folder"], dtype)
+    for ids, want in zip(case["prompts"], case["plain"][dtype]):
+        s = eng.acquire()
+        got = eng.step([s], [ids], [list(range(len(ids)))])
+        eng.release(s)
+        assert got.shape == want.shape
+        _close(got, want, dtype)
+    ids = case["prompts"][2]
+    taps, seen = [], []
+    P.forward(case["cfg"], case["w"], ids, taps)
+    sure = case["plain"][dtype][2].sure
+    upto = len(ids) if bool(sure.all()) else int((~sure).nonzero()[0])     # rows before a close call
+    eng.layer_tap = lambda i, h: seen.append(h.detach().cpu().to(torch.float64))
+    s = eng.acquire()
+    eng.step([s], [ids], [list(range(len(ids)))])
+    eng.release(s)
+    eng.layer_tap = None
+    assert len(seen) == len(taps) and upto >= 5
+    for got, want in zip(seen, taps):
+        tol = 3e-5 if dtype == "float32" else 4e-2
+        assert float((got - want)[:upto].abs().max()) < tol * float(want.abs().max())
+    eng.check_status()
+    eng.cache.check_canaries()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_last_tokens_one_by_one(case, dtype):
+    eng = _engine(case["folder"], dtype)
+    for ids, want in zip(case["prompts"], case["plain"][dtype]):
+        n = len(ids)
+        head = max(1, n - 40)
+        s = eng.acquire()
+        rows = [eng.step([s], [ids[:head]], [list(range(head))])]
+        for t in range(head, n):
+            rows.append(eng.step([s], [[ids[t]]], [[0]]))
+        eng.release(s)
+        _close(torch.cat(rows), want, dtype)
+    eng.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_token_by_token_from_the_first(case, dtype):
+    """Every token a step of its own, from position 0: the first tokens see the zeros before the
+    sequence in the convolution, empty recurrent states, and nothing but themselves (and the kept
+    first tokens, which they are) in attention."""
+    eng = _engine(case["folder"], dtype)
+    ids, want = case["prompts"][0], case["plain"][dtype][0]
+    s = eng.acquire()
+    rows = [eng.step([s], [[t]], [[0]]) for t in ids]
+    eng.release(s)
+    _close(torch.cat(rows), want, dtype)
+    eng.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("portion", [2, 3, 7, 15, 16, 17, 63, 64, 65])
+def test_prompts_in_portions(case, dtype, portion):
+    """Portions around the recurrences' chunk of 16 tokens and around a page of 64 positions."""
+    eng = _engine(case["folder"], dtype)
+    for ids, want in zip(case["prompts"][:4], case["plain"][dtype][:4]):
+        s = eng.acquire()
+        rows = []
+        for lo in range(0, len(ids), portion):
+            part = ids[lo:lo + portion]
+            rows.append(eng.step([s], [part], [list(range(len(part)))]))
+        eng.release(s)
+        _close(torch.cat(rows), want, dtype)
+    eng.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_unequal_batches_slots_reused(case, dtype):
+    """The prompts' first parts in one step, then one token each; a request that runs out of
+    tokens leaves the batch; the next batch starts in the slots, pages and state the first one
+    gave back.  Every request's logits equal those it has alone."""
+    eng = _engine(case["folder"], dtype, max_tokens=1024, max_seqs=4)
+    prompts, plain = case["prompts"], case["plain"][dtype]
+    for batch in ([0, 1, 2], [3, 4, 5, 6], [2, 0], [6, 2, 4]):
+        slots = {r: eng.acquire() for r in batch}
+        heads = {r: max(1, len(prompts[r]) - 9) for r in batch}
+        got = {r: [] for r in batch}
+        out = eng.step([slots[r] for r in batch], [prompts[r][:heads[r]] for r in batch],
+                       [list(range(heads[r])) for r in batch])
+        at = 0
+        for r in batch:
+            got[r].append(out[at:at + heads[r]])
+            at += heads[r]
+        pos = dict(heads)
+        live = [r for r in batch if pos[r] < len(prompts[r])]
+        while live:
+            out = eng.step([slots[r] for r in live], [[prompts[r][pos[r]]] for r in live],
+                           [[0]] * len(live))
+            for i, r in enumerate(live):
+                got[r].append(out[i:i + 1])
+                pos[r] += 1
+            live = [r for r in live if pos[r] < len(prompts[r])]
+        for r in batch:
+            _close(torch.cat(got[r]), plain[r], dtype)
+            eng.release(slots[r])
+    eng.check_status()
+    eng.cache.check_canaries()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_stale_slot_does_not_leak_into_the_next_request(case, dtype):
+    """A long request fills a slot's recurrent states, convolution inputs and pages; the slot is
+    given back and the next, short request in it must start from nothing."""
+    eng = _engine(case["folder"], dtype, max_tokens=512, max_seqs=1)
+    prompts, plain = case["prompts"], case["plain"][dtype]
+    for r in (2, 1, 4, 0, 4):
+        s = eng.acquire()
+        got = eng.step([s], [prompts[r]], [list(range(len(prompts[r])))])
+        eng.release(s)
+        _close(got, plain[r], dtype)
+    eng.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_step_and_wanted_rows_out_of_order(case, dtype):
+    """One request goes on by 20 tokens while two others go on by one, in the same step; only some
+    rows are wanted, so the per-token input after the last feed-forward is looked up for kept rows."""
+    eng = _engine(case["folder"], dtype)
+    prompts, plain = case["prompts"], case["plain"][dtype]
+    a, b, c = 2, 0, 6
+    sa, sb, sc = eng.acquire(), eng.acquire(), eng.acquire()
+    eng.step([sa, sb, sc], [prompts[a][:100], prompts[b][:30], prompts[c][:10]], [[], [], []])
+    out = eng.step([sb, sa, sc], [[prompts[b][30]], prompts[a][100:120], [prompts[c][10]]],
+                   [[0], [19, 3, 7], [0]])
+    _close(out[0:1], plain[b][30:31], dtype)
+    _close(out[1:4], plain[a][[119, 103, 107]], dtype)      # (rows in the order they were asked for)
+    _close(out[4:5], plain[c][10:11], dtype)
+    eng.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
+def test_long_decoding_past_the_windows(name, dtype):
+    """330 tokens: a prompt of 70, then one by one far past every window (and, where a layer keeps
+    nothing of the start, past its ring), with the recurrent layers' state and the kept first tokens
+    carried all the way; the same in portions of 50."""
+    folder = make_folder(name)
+    cfg, w = P.load_folder(folder)
+    ids = random_ids(330, cfg["vocab"], 91)
+    want = _plain(cfg, w, ids, dtype)
+    eng = _engine(folder, dtype, max_tokens=1024)
+    s = eng.acquire()
+    rows = [eng.step([s], [ids[:70]], [list(range(70))])]
+    for t in range(70, 330):
+        rows.append(eng.step([s], [[ids[t]]], [[0]]))
+    eng.release(s)
+    _close(torch.cat(rows), want, dtype)
+    eng2 = _engine(folder, dtype, max_tokens=1024, ring_step_tokens=1)
+    s = eng2.acquire()
+    rows = []
+    for lo in range(0, 330, 50):
+        part = ids[lo:lo + 50]
+        rows.append(eng2.step([s], [part], [list(range(len(part)))]))
+    _close(torch.cat(rows), want, dtype)
+    eng.check_status()
+    eng2.check_status()
+    eng2.cache.check_canaries()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_prompt_in_large_portions(dtype):
+    """430 tokens in portions of 200, 220 and 10: the later portions attend over the cache's pages
+    across the window's edge and the kept first tokens, the experts take their grouped path; then the
+    same prompt whole beside a short one."""
+    folder = make_folder("C")
+    cfg, w = P.load_folder(folder)
+    ids = random_ids(430, cfg["vocab"], 17)
+    want = _plain(cfg, w, ids, dtype)
+    eng = _engine(folder, dtype, max_tokens=2048)
+    s = eng.acquire()
+    rows, at = [], 0
+    for n in (200, 220, 10):
+        rows.append(eng.step([s], [ids[at:at + n]], [list(range(n))]))
+        at += n
+    eng.release(s)
+    _close(torch.cat(rows), want, dtype)
+    short = random_ids(33, cfg["vocab"], 18)
+    a, b = eng.acquire(), eng.acquire()
+    out = eng.step([b, a], [short, ids], [[32], [429, 0, 215]])
+    _close(out[0:1], _plain(cfg, w, short, dtype)[32:33], dtype)
+    _close(out[1:4], want[[429, 0, 215]], dtype)
+    eng.check_status()
+    eng.cache.check_canaries()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_generator(case, dtype):
+    from helpers import TOL
+    from minfer_b200.engine.generate import Generator
+    from minfer_b200.model import Model
+    from minfer_b200.sampling.params import SamplingParams
+    cfg, w = case["cfg"], case["w"]
+    prompts = [case["prompts"][0], case["prompts"][1], case["prompts"][6]]
+    gen = Generator(Model.from_folder(case["folder"], dtype, "cuda:0"), max_tokens=2048, max_batch=4)
+    got = gen.generate(prompts, 8, SamplingParams.greedy(), stop_token_ids=[])
+    for prompt, res in zip(prompts, got):
+        assert len(res.tokens) == 8
+        ids = list(prompt)
+        for tok in res.tokens:             # each token on the prefix the engine itself produced
+            plain = _plain(cfg, w, ids, dtype)
+            if not bool(plain.sure.all()):
+                break                      # a close call somewhere: the engine may rightly differ from here
+            logits = plain.logits[-1]
+            if dtype == "float32":
+                assert tok == int(torch.argmax(logits))
+            else:
+                slack = 2 * TOL["bfloat16"] * float(logits.abs().max())
+                assert float(logits[tok]) >= float(logits.max()) - slack
+            ids.append(tok)
+
+
+def test_command_line_generates(capsys):
+    from minfer_b200 import cli
+    folder = make_folder("B")
+    cfg, w = P.load_folder(folder)
+    rc = cli.main([folder, "5,17,3", "--greedy", "--repeat-penalty", "1.0", "-n", "6",
+                   "--dtype", "float32", "--stop", "100000"])
+    out = capsys.readouterr().out
+    assert rc == 0
+    want = P.generate_greedy(cfg, w, [5, 17, 3], 6)
+    assert " ".join(str(t) for t in want) in out
+    assert "Prefill: 3 tokens" in out and "Generated: 6 tokens" in out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_as_a_process(dtype):
+    """``bin/trace_run`` on a folder: two prompts of unequal length in one step, then one request's
+    last tokens one by one beside another that ends earlier; logits files against the plain
+    implementation."""
+    folder = make_folder("A")
+    cfg, w = P.load_folder(folder)
+    a, b = random_ids(70, cfg["vocab"], 1), random_ids(9, cfg["vocab"], 2)
+    plain = {"a": _plain(cfg, w, a, dtype), "b": _plain(cfg, w, b, dtype)}
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:60], "want": [0, 59]},
+                                     {"id": "b", "tokens": b[:7], "want": [6]}], "end": []}]
+    expect = {0: [("a", [0, 59]), ("b", [6])]}
+    for i in range(10):
+        entries = [{"id": "a", "tokens": [a[60 + i]], "want": [0] if i % 2 == 0 else []}]
+        rows = [("a", [60 + i])] if i % 2 == 0 else []
+        if i < 2:
+            entries.append({"id": "b", "tokens": [b[7 + i]], "want": [0]})
+            rows.append(("b", [7 + i]))
+        end = (["b"] if i == 1 else []) + (["a"] if i == 9 else [])
+        steps.append({"step": i + 1, "entries": entries, "end": end})
+        expect[i + 1] = rows
+    out = tempfile.mkdtemp()
+    root = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..")
+    proc = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder,
+                           "--dtype", dtype, "--out", out, "--max-tokens", "128"],
+                          input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True,
+                          text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(11)]
+    for step, rows in expect.items():
+        path = os.path.join(out, f"{step}.f32")
+        if not rows:
+            assert not os.path.exists(path)
+            continue
+        got = torch.from_numpy(np.fromfile(path, dtype="<f4").reshape(-1, cfg["vocab"]))
+        want = Plain.cat([plain[r][places] for r, places in rows])
+        _close(got, want, dtype)
+
+
+def _run_cuts(cfg, seed, dtype, n=90):
+    folder = make_folder("x", "bfloat16", cfg, seed)
+    cfg, w = P.load_folder(folder)
+    ids = random_ids(n, cfg["vocab"], 4)
+    want = _plain(cfg, w, ids, dtype)
+    eng = _engine(folder, dtype, max_tokens=512)
+    s = eng.acquire()
+    rows = [eng.step([s], [ids[:50]], [list(range(50))])]
+    rows.append(eng.step([s], [ids[50:53]], [[0, 1, 2]]))
+    for t in range(53, n):
+        rows.append(eng.step([s], [[ids[t]]], [[0]]))
+    eng.release(s)
+    _close(torch.cat(rows), want, dtype)
+    eng.check_status()
+    return eng
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_models_of_one_kind_of_layer(dtype):
+    """Retention only: the cache has no page group at all, only state.  Parallel layers only, in
+    another order, without any feed-forward.  A single layer."""
+    cfg = copy.deepcopy(ZAN_A)
+    cfg["layers"] = [cfg["layers"][1], cfg["layers"][2], copy.deepcopy(ZAN_B["layers"][0])]
+    cfg["width"] = 64
+    cfg["layers"][2]["mlp"]["router"]["top"] = 1
+    eng = _run_cuts(cfg, 51, dtype)
+    assert not eng.cache.groups
+    cfg = copy.deepcopy(ZAN_A)
+    cfg["layers"] = [dict(cfg["layers"][3], mlp=None), dict(cfg["layers"][0], mlp=None)]
+    _run_cuts(cfg, 52, dtype)
+    cfg = copy.deepcopy(ZAN_C)
+    cfg["layers"] = [cfg["layers"][0]]
+    _run_cuts(cfg, 53, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_that_are_one(dtype):
+    """One head of everything, one key/value head, one state number per channel, a step-size rank of
+    one, one tap, one expert of which one is used, one identity expert, a token input one wide, a
+    window of one position that keeps one first token, scales and factors that are 1."""
+    cfg = {
+        "architecture": "Zanelorn", "vocab": 61, "width": 32, "norm": {"eps": 1e-6},
+        "residual_mult": 1.0, "embedding": {"scale": 1.0}, "token_side": {"dim": 1},
+        "layers": [
+            {"type": "retention", "mixer": {"heads": 1, "dim": 8, "vdim": 1, "decay": [1.0],
+                                            "rot": {"base": 100.0, "dims": 2}},
+             "mlp": {"kind": "moe", "expert": {"ff": 8, "limit": 1.0},
+                     "router": {"experts": 1, "identity": 1, "top": 1}, "shared": {"ff": 1, "limit": 1.0}}},
+            {"type": "parallel",
+             "mixer": {"left": {"heads": 1, "kv_heads": 1, "dim": 2, "vdim": 1, "scale": 1.0,
+                                "mask": {"size": 1, "keep_first": 1},
+                                "rot": {"base": 10.0, "dims": 2, "scaling": {"factor": 1.0}}},
+                       "right": {"inner": 1, "state": 1, "dt_rank": 1, "conv": 1},
+                       "left_scale": 1.0, "right_scale": 1.0},
+             "mlp": {"kind": "dense", "ff": 1}},
+        ],
+    }
+    _run_cuts(cfg, 54, dtype, n=70)
+
+
+def test_matrices_stored_in_32_bit_run_in_the_bfloat16_engine():
+    """A checkpoint whose matrices are float32 keeps them so in the bfloat16 engine (FP32-pipe
+    products, bfloat16 cache and attention): every mixer and feed-forward takes the mix."""
+    folder = make_folder("A", "float32")
+    cfg, w = P.load_folder(folder)
+    ids = random_ids(75, cfg["vocab"], 8)
+    want = _plain(cfg, w, ids, "bfloat16")
+    eng = _engine(folder, "bfloat16", max_tokens=512)
+    s = eng.acquire()
+    rows = [eng.step([s], [ids[:60]], [list(range(60))])]
+    rows += [eng.step([s], [[t]], [[0]]) for t in ids[60:]]
+    eng.release(s)
+    _close(torch.cat(rows), want, "bfloat16")
+    eng.check_status()
