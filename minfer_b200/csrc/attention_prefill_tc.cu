@@ -75,6 +75,9 @@ struct FaArgs {
     //   0: none); a learned score of the sink per head instead of 0
     float cap_raw, inv_cap_raw;
     const float* sink_logit;  // [n_heads] or null
+    //   and keys at positions below keep_first that stay visible beyond the window (linear
+    //   caches only): their key tiles are walked first, before the window's
+    int keep_first;
 };
 
 #define FA_TAB_PAD 256        // zeros on either side of the bias table (indices of masked scores)
@@ -272,7 +275,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     const bool has1 = ke[1] > kb[1];
     const int lo = kb[0], hi = has1 ? ke[1] : ke[0];
-    const int n_tiles = hi - lo;
+    // The key tiles in the order they are walked: `kept` tiles of the first keys that lie before
+    // the CTA's first window tile, then lo .. hi - 1.  Query tile t takes part in the tiles of its
+    // own window, [kb[t], ke[t]), and in the tiles below it that hold kept keys, [0, kfirst[t]).
+    const int kept_all = (MOD && a.keep_first > 0) ? (a.keep_first + FA_KEYS - 1) / FA_KEYS : 0;
+    const int kept = min(kept_all, lo);
+    const int kfirst[2] = {min(kept_all, kb[0]), min(kept_all, kb[1])};
+    const int n_tiles = kept + hi - lo;
+    auto tile_at = [&](int i) { return i < kept ? i : lo + (i - kept); };
+    auto takes_part = [&](int t, int i) {
+        const int j = tile_at(i);
+        return (t == 0 || has1) && (j < kfirst[t] || (j >= kb[t] && j < ke[t]));
+    };
 
     if (tid == 0) {
         fa_bar_init(fa_smem(q_full), 1);
@@ -329,7 +343,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 int y[2];
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const int p = (lo + i) * FA_KEYS + h * MF_PAGE;
+                    const int p = tile_at(i) * FA_KEYS + h * MF_PAGE;
                     const int idx = (a.ring > 0 ? p % a.ring : p) >> 6;
                     int page = idx < a.table_stride ? a.page_table[(size_t)seq * a.table_stride + idx] : 0;
                     if (page < 0) page = 0;
@@ -349,7 +363,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                                fa_smem(&v_full[st]));
                 continue;
             }
-            const int key0 = tok0 + (lo + i) * FA_KEYS;
+            const int key0 = tok0 + tile_at(i) * FA_KEYS;
             if (!fa_wait(fa_smem(&k_empty[st]), free_parity, abort_flag)) break;
             fa_expect_tx(fa_smem(&k_full[st]), T_BYTES);
             for (int c = 0; c < NB; ++c)
@@ -387,14 +401,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             fa_fence_after();
 #pragma unroll
             for (int t = 0; t < 2; ++t)
-                if (lo >= kb[t] && lo < ke[t]) issue_qk(t, 0);
+                if (takes_part(t, 0)) issue_qk(t, 0);
             fa_commit(fa_smem(&k_empty[0]));
         }
         // per key tile and query tile: O += P V for this key tile as soon as its probabilities
         // are there, then at once S = Q K^T for the next key tile into the same columns; while
         // one query tile is in its softmax the tensor cores work for the other
         for (int i = 0; i < n_tiles && ok; ++i) {
-            const int j = lo + i;
             const bool next = i + 1 < n_tiles;
             ok = fa_wait(fa_smem(&v_full[i & 1]), (uint32_t)((i >> 1) & 1), abort_flag);
             if (ok && next) ok = fa_wait(fa_smem(&k_full[(i + 1) & 1]), (uint32_t)(((i + 1) >> 1) & 1), abort_flag);
@@ -403,8 +416,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const uint32_t v_addr = fa_smem(v_s + (i & 1) * T_BYTES);
 #pragma unroll
             for (int t = 0; t < 2; ++t) {
-                const bool cur = j >= kb[t] && j < ke[t];
-                const bool nxt = next && j + 1 >= kb[t] && j + 1 < ke[t];
+                const bool cur = takes_part(t, i);
+                const bool nxt = next && takes_part(t, i + 1);
                 if (cur) {
                     ok = fa_wait(fa_smem(&p_full[t]), (uint32_t)(done[t] & 1), abort_flag);
                     if (!ok) break;
@@ -417,7 +430,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     ++done[t];
                 }
                 if (nxt) issue_qk(t, i + 1);
-                else if (cur) fa_commit(fa_smem(&o_done[t]));
+                else if (cur && tile_at(i) >= kb[t]) fa_commit(fa_smem(&o_done[t]));   // (a window's tiles follow the kept ones)
             }
             if (!ok) break;
             fa_commit(fa_smem(&v_empty[i & 1]));
@@ -446,13 +459,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int row_lo = MOD ? fa_first_key(qpos, 0, a.chunk) : 0;              // chunk's first key
         const int warp_lo = MOD ? fa_first_key(wpos + 31, 0, a.chunk) : 0;
         bool ok = true;
-        for (int j = kb_t; j < ke_t; ++j) {
-            const int c = j - kb_t;
+        const int kf_t = t ? kfirst[1] : kfirst[0];
+        const int n_mine = ke_t > kb_t ? kf_t + ke_t - kb_t : 0;      // key tiles this query tile takes part in
+        for (int c = 0; c < n_mine; ++c) {
+            const int j = c < kf_t ? c : kb_t + (c - kf_t);
             const int key0 = j * FA_KEYS;
             // S of this key tile is complete, and with it every earlier product of this query tile
             if (!fa_wait(fa_smem(&s_full[t]), (uint32_t)(c & 1), abort_flag)) { ok = false; break; }
             fa_fence_after();
-            const bool need_mask = key0 + FA_KEYS - 1 > wpos || key0 + FA_KEYS > key_end ||
+            const bool need_mask = c < kf_t || key0 + FA_KEYS - 1 > wpos || key0 + FA_KEYS > key_end ||
                                    (a.window > 0 && key0 < wpos + 31 - a.window + 1) ||
                                    (MOD && key0 < warp_lo);
             // the whole row of S (128 scores) into registers, masked by position where the tile
@@ -489,7 +504,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                 for (int i = 0; i < FA_KEYS; ++i) {
                     const int key = key0 + i;
-                    const bool vis = key <= qpos && key < key_end && (a.window == 0 || qpos - key < a.window) &&
+                    const bool vis = key <= qpos && key < key_end &&
+                                     (a.window == 0 || qpos - key < a.window || (MOD && key < a.keep_first)) &&
                                      (!MOD || key >= row_lo);
                     if (!vis) sr[i] = 0xff800000u;            // -inf
                 }
@@ -724,9 +740,10 @@ extern "C" int mf_sink_attention_tc(const void* q, const void* k, const void* v,
                                     void* out, const float* r1, const float* r2, int n_tokens, int n_seqs,
                                     int max_len, int n_heads, int n_kv, int hd, int window, int chunk,
                                     int sink, float scale, long long cache_pages, const float* sink_logit,
-                                    float softcap, unsigned* status, cudaStream_t stream) {
+                                    float softcap, int keep_first, unsigned* status, cudaStream_t stream) {
     if (n_seqs <= 0 || max_len <= 0 || n_tokens <= 0) return 0;
     if (softcap < 0.0f) return MF_ERR_ARGUMENT;
+    if (keep_first < 0 || (keep_first > 0 && (ring > 0 || chunk > 0 || r1 != nullptr))) return MF_ERR_UNSUPPORTED;
     if ((hd != 64 && hd != 128) || n_kv <= 0 || n_heads % n_kv != 0) return MF_ERR_UNSUPPORTED;
     if (n_seqs > 65535 || (max_len + FA_CTA_Q - 1) / FA_CTA_Q > 65535) return MF_ERR_UNSUPPORTED;
     if (((uintptr_t)q & 15) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15) || ((uintptr_t)out & 15))
@@ -750,6 +767,7 @@ extern "C" int mf_sink_attention_tc(const void* q, const void* k, const void* v,
     a.seq_end = seq_end; a.page_table = page_table; a.table_stride = table_stride; a.ring = ring;
     a.chunk = chunk; a.sink = sink ? 1 : 0; a.r1 = r1; a.r2 = r2;
     a.sink_logit = sink_logit;
+    a.keep_first = window > 0 ? keep_first : 0;
     a.cap_raw = softcap > 0.0f ? softcap / scale : 0.0f;
     a.inv_cap_raw = softcap > 0.0f ? scale / softcap : 0.0f;
     int reach = chunk;

@@ -451,6 +451,7 @@ struct SinkMmaArgs {
     const float* r1;          // [n_heads] or null
     const float* r2;
     int n_heads, n_kv, hd, vd, window, chunk, sink;
+    int keep_first;           // > 0: keys at positions below it stay visible beyond the window
     int tab_n;                // entries of the bias table (0: the bias is computed per score)
     float scale_log2;         // scale * log2(e)
     const float* sink_logit;  // [n_heads] score of the sink, or null for 0
@@ -567,7 +568,12 @@ sink_attention_mma_kernel(SinkMmaArgs a) {
         copy_v.load(v_s + (uint32_t)(buf * 64 * VDP * 2), vb, vs, end - key0);
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    load_tile(kt_begin, 0);
+    // the key tiles a CTA walks: those of the kept first keys that lie before the window's first
+    // tile, then the window's
+    const int kept_tiles = a.keep_first > 0 ? min((a.keep_first + SM_KEYS - 1) / SM_KEYS, kt_begin) : 0;
+    const int n_iter = kept_tiles + kt_end - kt_begin + 1;
+    auto tile_of = [&](int it) { return it < kept_tiles ? it : kt_begin + (it - kept_tiles); };
+    load_tile(tile_of(0), 0);
 
     // the sink starts the running maximum at its score (0, or the head's learned one)
     const float sink2 = (a.sink && a.sink_logit) ? a.sink_logit[head] * 1.4426950408889634f : 0.0f;
@@ -605,10 +611,11 @@ sink_attention_mma_kernel(SinkMmaArgs a) {
 #pragma unroll
     for (int i = 0; i < VDP / 16; ++i) v_col[i] = (uint32_t)(((2 * i + (lane >> 4)) ^ (lane & 7)) * 16);
 
-    for (int kt = kt_begin; kt <= kt_end; ++kt) {
-        const int buf = (kt - kt_begin) & 1;
-        if (kt < kt_end) {                                        // prefetch the next tile
-            load_tile(kt + 1, buf ^ 1);
+    for (int it = 0; it < n_iter; ++it) {
+        const int kt = tile_of(it);
+        const int buf = it & 1;
+        if (it + 1 < n_iter) {                                    // prefetch the next tile
+            load_tile(tile_of(it + 1), buf ^ 1);
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
             asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -643,7 +650,7 @@ sink_attention_mma_kernel(SinkMmaArgs a) {
                 const int d = row_p[r] - key;
                 float x = a.cap_log2 > 0.0f ? a.cap_log2 * sink_tanh(s[nt][e] * a.scale_over_cap)
                                             : s[nt][e] * a.scale_log2;
-                const bool vis = all_visible || (d >= 0 && key >= row_lo[r]);
+                const bool vis = all_visible || (d >= 0 && (key >= row_lo[r] || key < a.keep_first));
                 if (has_bias && vis)
                     x -= a.tab_n > 0 ? tab[d] : r1 * __log2f(fmaf(r2, (float)d, 1.0f));
                 s[nt][e] = vis ? x : -INFINITY;
@@ -753,8 +760,9 @@ extern "C" int mf_sink_attention_mma(const void* q, const void* k, const void* v
                                      const float* r1, const float* r2, int n_seqs, int max_new,
                                      int n_heads, int n_kv, int hd, int vd, int window, int chunk,
                                      int sink, float scale, const float* sink_logit, float softcap,
-                                     cudaStream_t stream) {
+                                     int keep_first, cudaStream_t stream) {
     if (n_seqs <= 0 || max_new <= 0) return 0;
+    if (keep_first < 0 || (keep_first > 0 && (ring > 0 || chunk > 0 || r1 != nullptr))) return MF_ERR_UNSUPPORTED;
     if (softcap < 0.0f) return MF_ERR_ARGUMENT;
     if (!mf_sink_attention_mma_supported(hd, vd) || n_kv <= 0 || n_heads % n_kv != 0) return MF_ERR_UNSUPPORTED;
     if (n_heads > 65535 || n_seqs > 65535 || window < 0 || chunk < 0) return MF_ERR_UNSUPPORTED;
@@ -766,6 +774,7 @@ extern "C" int mf_sink_attention_mma(const void* q, const void* k, const void* v
     a.table_stride = table_stride; a.ring = ring; a.out = (__nv_bfloat16*)out; a.r1 = r1; a.r2 = r2;
     a.n_heads = n_heads; a.n_kv = n_kv; a.hd = hd; a.vd = vd; a.window = window; a.chunk = chunk;
     a.sink = sink ? 1 : 0;
+    a.keep_first = window > 0 ? keep_first : 0;
     int reach = 0;
     if (chunk > 0) reach = chunk;
     if (window > 0 && (reach == 0 || window < reach)) reach = window;
@@ -813,6 +822,7 @@ struct SinkDecodeArgs {
     const float* r1;
     const float* r2;
     int n_heads, n_kv, hd, vd, window, chunk, sink;
+    int keep_first;           // > 0: keys at positions below it stay visible beyond the window
     int tiles_per_cta, n_splits;
     int n_bufs;               // buffers a warp has: 2, or 1 when it takes one tile only
     float scale_log2;
@@ -856,8 +866,13 @@ __global__ void __launch_bounds__(SD_WARPS * 32) sink_attention_decode_kernel(Si
     const int b = a.row_seq[row];
     const int pos = a.row_pos[row];
     const int lo = sink_first_key(pos, a.window, a.chunk);
-    const int tile_lo = lo / SD_KEYS + split * a.tiles_per_cta;   // this CTA's first tile
-    const int tile_hi = min(pos / SD_KEYS, tile_lo + a.tiles_per_cta - 1);   // inclusive
+    // the tiles a query sees, numbered in the order they are walked: those of the kept first keys
+    // that lie before the window's first tile, then the window's
+    const int first_tile = lo / SD_KEYS;
+    const int kept_tiles = a.keep_first > 0 ? min((a.keep_first + SD_KEYS - 1) / SD_KEYS, first_tile) : 0;
+    auto real_tile = [&](int vt) { return vt < kept_tiles ? vt : first_tile + (vt - kept_tiles); };
+    const int tile_lo = split * a.tiles_per_cta;                  // this CTA's first tile (in that order)
+    const int tile_hi = min(kept_tiles + pos / SD_KEYS - first_tile, tile_lo + a.tiles_per_cta - 1);   // inclusive
     const bool has_bias = a.r1 != nullptr;
     // this thread's two rows of the product are the group's heads g and g + 8
     float r1v[2] = {0.0f, 0.0f}, r2v[2] = {0.0f, 0.0f};
@@ -880,7 +895,7 @@ __global__ void __launch_bounds__(SD_WARPS * 32) sink_attention_decode_kernel(Si
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     int tile = tile_lo + warp;
-    if (tile <= tile_hi) load_tile(tile, 0);
+    if (tile <= tile_hi) load_tile(real_tile(tile), 0);
 
     float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.0f, 0.0f};
     float o[VDP / 8][4];
@@ -911,7 +926,7 @@ __global__ void __launch_bounds__(SD_WARPS * 32) sink_attention_decode_kernel(Si
     for (int it = 0; tile <= tile_hi; tile += SD_WARPS, ++it) {
         const int buf = it & 1;
         if (tile + SD_WARPS <= tile_hi) {
-            load_tile(tile + SD_WARPS, buf ^ 1);
+            load_tile(real_tile(tile + SD_WARPS), buf ^ 1);
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
             asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -932,14 +947,14 @@ __global__ void __launch_bounds__(SD_WARPS * 32) sink_attention_decode_kernel(Si
                 sm_mma16816(s[2 * np + 1], qa[ks], b2, b3);
             }
         }
-        const int key0 = tile * SD_KEYS;
+        const int key0 = real_tile(tile) * SD_KEYS;
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int key = key0 + nt * 8 + 2 * t + (e & 1);
                 const int d = pos - key;
-                const bool vis = d >= 0 && key >= lo;
+                const bool vis = d >= 0 && (key >= lo || key < a.keep_first);
                 float x = a.cap_log2 > 0.0f ? a.cap_log2 * sink_tanh(s[nt][e] * a.scale_over_cap)
                                             : s[nt][e] * a.scale_log2;
                 if (has_bias && vis) x -= r1v[e >> 1] * __log2f(fmaf(r2v[e >> 1], (float)d, 1.0f));
@@ -1123,8 +1138,9 @@ extern "C" int mf_sink_attention_decode(const void* q, const void* k_cache, cons
                                         const float* r2, int rows, int n_heads, int n_kv, int hd,
                                         int vd, int window, int chunk, int sink, float scale,
                                         int reach_keys, const float* sink_logit, float softcap,
-                                        cudaStream_t stream) {
+                                        int keep_first, cudaStream_t stream) {
     if (rows <= 0) return 0;
+    if (keep_first < 0 || (keep_first > 0 && (ring > 0 || chunk > 0))) return MF_ERR_UNSUPPORTED;
     if (softcap < 0.0f) return MF_ERR_ARGUMENT;
     if (!mf_sink_attention_mma_supported(hd, vd) || n_kv <= 0 || n_heads % n_kv != 0) return MF_ERR_UNSUPPORTED;
     const int head_blocks = n_kv * ((n_heads / n_kv + 15) / 16);      // CTAs per (split, query)
@@ -1137,6 +1153,7 @@ extern "C" int mf_sink_attention_decode(const void* q, const void* k_cache, cons
     a.out = (__nv_bfloat16*)out; a.partial = partial; a.r1 = r1; a.r2 = r2;
     a.n_heads = n_heads; a.n_kv = n_kv; a.hd = hd; a.vd = vd; a.window = window; a.chunk = chunk;
     a.sink = sink ? 1 : 0;
+    a.keep_first = window > 0 ? keep_first : 0;
     a.scale_log2 = scale * 1.4426950408889634f;
     a.sink_logit = sink_logit;
     a.cap_log2 = softcap * 1.4426950408889634f;

@@ -153,12 +153,13 @@ def _sig_attention_sink(lib: ctypes.CDLL) -> None:
 
     lib.mf_sink_attention_mma_supported.argtypes = [c_int, c_int]
     lib.mf_sink_attention_mma.argtypes = ([c_void_p] * 6 + [c_int, c_int] + [c_void_p] * 3 +
-                                          [c_int] * 9 + [c_float, c_void_p, c_float, c_void_p])
+                                          [c_int] * 9 + [c_float, c_void_p, c_float, c_int, c_void_p])
 
 
     lib.mf_sink_decode_plan.argtypes = [c_int, c_int, c_int, c_void_p, c_void_p]
     lib.mf_sink_attention_decode.argtypes = ([c_void_p] * 6 + [c_int, c_int] + [c_void_p] * 4 +
-                                             [c_int] * 8 + [c_float, c_int, c_void_p, c_float, c_void_p])
+                                             [c_int] * 8 + [c_float, c_int, c_void_p, c_float, c_int,
+                                                            c_void_p])
 
 
 def _sig_sampling(lib: ctypes.CDLL) -> None:
@@ -204,7 +205,7 @@ def _sig_attention_prefill_tc(lib: ctypes.CDLL) -> None:
 
 
     lib.mf_sink_attention_tc.argtypes = ([c_void_p] * 6 + [c_int, c_int] + [c_void_p] * 3 + [c_int] * 9 +
-                                         [c_float, c_longlong, c_void_p, c_float, c_void_p, c_void_p])
+                                         [c_float, c_longlong, c_void_p, c_float, c_int, c_void_p, c_void_p])
 
 
 def _sig_recurrent(lib: ctypes.CDLL) -> None:
@@ -1603,7 +1604,7 @@ def sink_attention_mma(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seq
                        r2: Optional[torch.Tensor], n_rows: int, max_row_tokens: int, n_heads: int,
                        n_kv: int, head_dim: int, value_dim: int, window: int, chunk: int, sink: bool,
                        scale: float, sink_logit: Optional[torch.Tensor] = None,
-                       softcap: float = 0.0) -> None:
+                       softcap: float = 0.0, keep_first: int = 0) -> None:
     """The step's packed queries (sequence b brings tokens cu_seqlens[b] .. cu_seqlens[b+1]-1)
     on tensor cores.  ``page_table`` None: ``k``, ``v`` are the step's own packed rows and every
     sequence starts at position 0; else they are the cache and sequence b ends at
@@ -1617,7 +1618,8 @@ def sink_attention_mma(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seq
         _i32(seq_end, "seq_end"), _i32(page_table, "page_table"), int(table_stride), int(ring),
         _ptr(out, "out"), _f32(r1, "r1"), _f32(r2, "r2"), int(n_rows), int(max_row_tokens), n_heads,
         n_kv, head_dim, value_dim, int(window), int(chunk), 1 if sink else 0, float(scale),
-        _f32(sink_logit, "sink_logit"), float(softcap), _stream()), "sink_attention_mma")
+        _f32(sink_logit, "sink_logit"), float(softcap), int(keep_first), _stream()),
+        "sink_attention_mma")
 
 
 def sink_attention_tc_supported(dtype: torch.dtype, head_dim: int, value_dim: int) -> bool:
@@ -1631,7 +1633,7 @@ def sink_attention_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seql
                       r2: Optional[torch.Tensor], n_rows: int, max_row_tokens: int, n_heads: int,
                       n_kv: int, head_dim: int, window: int, chunk: int, sink: bool, scale: float,
                       status: torch.Tensor, sink_logit: Optional[torch.Tensor] = None,
-                      softcap: float = 0.0) -> None:
+                      softcap: float = 0.0, keep_first: int = 0) -> None:
     """``sink_attention_mma``'s job on the 5th-generation tensor cores (tcgen05, tensor memory):
     the step's packed queries over the step's own keys (``page_table`` None) or over the cache."""
     n = q.shape[0]
@@ -1645,8 +1647,8 @@ def sink_attention_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seql
         _i32(seq_end, "seq_end"), _i32(page_table, "page_table"), int(table_stride), int(ring),
         _ptr(out, "out"), _f32(r1, "r1"), _f32(r2, "r2"), n, int(n_rows), int(max_row_tokens),
         n_heads, n_kv, head_dim, int(window), int(chunk), 1 if sink else 0, float(scale), int(pages),
-        _f32(sink_logit, "sink_logit"), float(softcap), _i32(status, "status"), _stream()),
-        "sink_attention_tc")
+        _f32(sink_logit, "sink_logit"), float(softcap), int(keep_first), _i32(status, "status"),
+        _stream()), "sink_attention_tc")
 
 
 _SINK_PLANS: dict = {}
@@ -1671,7 +1673,7 @@ def sink_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch
                           r1: Optional[torch.Tensor], r2: Optional[torch.Tensor], n_heads: int,
                           n_kv: int, head_dim: int, value_dim: int, window: int, chunk: int,
                           sink: bool, scale: float, reach_keys: int,
-                          sink_logit: Optional[torch.Tensor] = None, softcap: float = 0.0) -> None:
+                          sink_logit: Optional[torch.Tensor] = None, softcap: float = 0.0, keep_first: int = 0) -> None:
     """Every row of ``q`` a query at its own position over the paged cache, on tensor cores
     (bfloat16; the query heads of a key/value head in blocks of up to 16).  ``reach_keys``: the most keys a query
     sees (its chunk or window, or the longest sequence's length)."""
@@ -1691,7 +1693,7 @@ def sink_attention_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch
         _i32(row_pos, "row_pos"), _i32(page_table, "page_table"), int(table_stride), int(ring),
         _ptr(out, "out"), _f32(partial, "partial"), _f32(r1, "r1"), _f32(r2, "r2"), rows, n_heads,
         n_kv, head_dim, value_dim, int(window), int(chunk), 1 if sink else 0, float(scale),
-        int(reach_keys), _f32(sink_logit, "sink_logit"), float(softcap), _stream()),
+        int(reach_keys), _f32(sink_logit, "sink_logit"), float(softcap), int(keep_first), _stream()),
         "sink_attention_decode", 2 if splits > 1 else 1)
 
 

@@ -73,6 +73,17 @@ class ScoreSpec:
         return min(bounds) if bounds else 0
 
 
+def decode_reach(spec: ScoreSpec, max_end: int) -> int:
+    """The most keys a single query sees: its reach, the window plus the kept first keys (and a
+    tile's worth for the two stretches' ragged ends), or the longest sequence."""
+    reach = spec.reach()
+    if reach > 0:
+        return reach
+    if spec.window > 0 and spec.keep_first > 0:
+        return min(max_end, spec.window + spec.keep_first + 64)
+    return max_end
+
+
 def scored_attention(spec: ScoreSpec, q: torch.Tensor, k_step: Optional[torch.Tensor],
                      v_step: Optional[torch.Tensor], cache, ctx: StepContext, o: torch.Tensor) -> None:
     """o = attention of the step's queries ``q`` [tokens, heads, head_dim] (already normed,
@@ -86,20 +97,24 @@ def scored_attention(spec: ScoreSpec, q: torch.Tensor, k_step: Optional[torch.Te
     r1, r2 = spec.r1, spec.r2
     cap, sl = spec.softcap, spec.sink_logit
     keep = spec.keep_first if spec.window > 0 else 0
-    tensor_cores = (K.sink_attention_mma_supported(act, hd, vd) and not FORCE_GENERIC
-                    and keep == 0)         # kept first tokens: the generic kernels
+    if keep > 0 and (spec.chunk > 0 or r1 is not None or (cache is not None and cache.ring)):
+        raise K.KernelError("kept first tokens go with a window on a cache that keeps every position, "
+                            "without a chunk mask or a distance bias")
+    tensor_cores = K.sink_attention_mma_supported(act, hd, vd) and not FORCE_GENERIC
     # prompts: the tcgen05 kernel where keys and values have one size it takes, else mma.sync
     tcgen05 = (tensor_cores and PROMPT_KERNEL != "mma" and spec.scale > 0.0
                and K.sink_attention_tc_supported(act, hd, vd))
     if own_kv and tcgen05:
         K.sink_attention_tc(q, k_step, v_step, ctx.cu_seqlens, None, None, 0, 0, o, r1, r2,
                             ctx.n_rows, ctx.max_row_tokens, nh, nk, hd, spec.window, spec.chunk,
-                            spec.sink, spec.scale, ctx.status, sink_logit=sl, softcap=cap)
+                            spec.sink, spec.scale, ctx.status, sink_logit=sl, softcap=cap,
+                            keep_first=keep)
         return
     if own_kv and tensor_cores:
         K.sink_attention_mma(q, k_step, v_step, ctx.cu_seqlens, None, None, 0, 0, o, r1, r2,
                              ctx.n_rows, ctx.max_row_tokens, nh, nk, hd, vd, spec.window,
-                             spec.chunk, spec.sink, spec.scale, sink_logit=sl, softcap=cap)
+                             spec.chunk, spec.sink, spec.scale, sink_logit=sl, softcap=cap,
+                             keep_first=keep)
         return
     if own_kv:
         K.sink_attention_packed(q, k_step, v_step, ctx.token_row, ctx.positions, ctx.cu_seqlens, o,
@@ -117,21 +132,22 @@ def scored_attention(spec: ScoreSpec, q: torch.Tensor, k_step: Optional[torch.Te
         K.sink_attention_tc(q, cache.k, cache.v, ctx.cu_seqlens, ctx.seq_end, cache.page_table,
                             cache.table_stride, cache.ring, o, r1, r2, ctx.n_rows,
                             ctx.max_row_tokens, nh, nk, hd, spec.window, spec.chunk, spec.sink,
-                            spec.scale, ctx.status, sink_logit=sl, softcap=cap)
+                            spec.scale, ctx.status, sink_logit=sl, softcap=cap, keep_first=keep)
         return
     if tensor_cores and not ctx.single_token and ctx.n_tokens >= PAGED_PROMPT_MIN_TOKENS:
         # rows of several tokens: query tiles of the step's rows over the cache's pages
         K.sink_attention_mma(q, cache.k, cache.v, ctx.cu_seqlens, ctx.seq_end, cache.page_table,
                              cache.table_stride, cache.ring, o, r1, r2, ctx.n_rows,
                              ctx.max_row_tokens, nh, nk, hd, vd, spec.window, spec.chunk,
-                             spec.sink, spec.scale, sink_logit=sl, softcap=cap)
+                             spec.sink, spec.scale, sink_logit=sl, softcap=cap, keep_first=keep)
         return
     if tensor_cores:
         # single queries: the heads of a key/value head are the rows of the product
         K.sink_attention_decode(q, cache.k, cache.v, ctx.token_row, ctx.positions,
                                 cache.page_table, cache.table_stride, cache.ring, o, r1, r2, nh,
                                 nk, hd, vd, spec.window, spec.chunk, spec.sink, spec.scale,
-                                reach if reach > 0 else ctx.max_end, sink_logit=sl, softcap=cap)
+                                decode_reach(spec, ctx.max_end), sink_logit=sl, softcap=cap,
+                                keep_first=keep)
         return
     K.sink_attention_paged(q, cache.k, cache.v, ctx.token_row, ctx.positions, cache.page_table,
                            cache.table_stride, cache.ring, o, r1, r2, nh, nk, hd, vd, spec.window,

@@ -326,15 +326,24 @@ def _marked(n, nh, nk, hd, vd, marks, g, dt):
 @pytest.mark.parametrize("hd,vd,nh,nk,window,keep", [(16, 24, 4, 2, 20, 3), (64, 64, 6, 3, 100, 6),
                                                      (12, 12, 3, 3, 65, 1), (8, 8, 3, 1, 9, 30),
                                                      (128, 128, 2, 1, 40, 70), (64, 64, 2, 2, 64, 64)])
-@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
-def test_kept_first_tokens_and_the_window_edge(hd, vd, nh, nk, window, keep, dt):
+@pytest.mark.parametrize("dt,kernel", [(torch.float32, "any"), (torch.bfloat16, "any"),
+                                       (torch.bfloat16, "mma"), (torch.bfloat16, "generic")])
+def test_kept_first_tokens_and_the_window_edge(hd, vd, nh, nk, window, keep, dt, kernel, monkeypatch):
     """Marks: the last kept token (keep - 1), the first one not kept (keep), and one in the middle.
     Far queries see mark keep - 1 for ever; mark keep is seen for exactly ``window`` queries; the
     middle one is seen up to its window's edge and not one query longer.  Whole prompts over
-    packed keys, then every query over the paged cache with scattered pages."""
+    packed keys, then the last 200 queries as one step over the paged cache with scattered pages,
+    then single queries at the edges."""
     from minfer_b200.kernels import api as K
     from minfer_b200.parts.sink_attention import ScoreSpec, scored_attention
+    from minfer_b200.parts import sink_attention
     from minfer_b200.parts.base import CacheView, StepContext
+    # bfloat16: the tensor-memory kernel where the sizes allow (keys and values of 64 or 128), the
+    # mma.sync kernels otherwise and when asked for, the generic kernel for the rest and when asked for
+    if kernel == "mma":
+        monkeypatch.setattr(sink_attention, "PROMPT_KERNEL", "mma")
+    if kernel == "generic":
+        monkeypatch.setattr(sink_attention, "FORCE_GENERIC", True)
     g = torch.Generator().manual_seed(hd + window + keep)
     n = 400
     mid = 2 * window + keep + 77
@@ -377,7 +386,7 @@ def test_kept_first_tokens_and_the_window_edge(hd, vd, nh, nk, window, keep, dt)
     o = torch.empty(n + 5, nh * vd, dtype=dt, device=DEV)
     scored_attention(spec, q2, k2, v2, None, c, o)
     check(o[5:])
-    # over the paged cache: pages scattered, stale values elsewhere; the last 150 queries in a step
+    # over the paged cache: pages scattered, stale values elsewhere; the last 200 queries in a step
     # of several tokens, then each of them alone as a step of one token a row
     n_pages = (n + 63) // 64
     kc = torch.randn(n_pages + 5, nk, 64, hd, generator=g).to(dt).to(DEV)
@@ -387,7 +396,7 @@ def test_kept_first_tokens_and_the_window_edge(hd, vd, nh, nk, window, keep, dt)
         kc[order[p // 64], :, p % 64] = k[p].to(DEV)
         vc[order[p // 64], :, p % 64] = v[p].to(DEV)
     cache = CacheView(k=kc, v=vc, page_table=_i32([order]), table_stride=n_pages, ring=0)
-    tail = 150
+    tail = 200
     c = ctx(False, [tail], list(range(n - tail, n)), [n])
     o = torch.empty(tail, nh * vd, dtype=dt, device=DEV)
     scored_attention(spec, q[n - tail:].contiguous().to(DEV), None, None, cache, c, o)

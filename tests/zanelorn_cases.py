@@ -99,7 +99,7 @@ def loud_weights(folder: str, seed: int) -> None:
     for name in sorted(w):
         t = w[name]
         if name.endswith("mlp.router"):
-            new = rnd(t.shape, 0.0, 0.7)
+            new = rnd(t.shape, 0.0, 2.0)
         elif name.endswith("mlp.correction"):
             new = rnd(t.shape, 0.0, 0.05)
         elif name.endswith("shared.sg"):
