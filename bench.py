@@ -1025,6 +1025,284 @@ def workload_bedarax(args) -> int:
     return 0
 
 
+# ------------------------------------------------------------------------------------------
+# --workload zanelorn: the Zanelorn design beside the Qwen2 decoder at equal width and layers
+# ------------------------------------------------------------------------------------------
+# (name, width, attention heads, kv heads, head size, feed-forward width, retention heads, window,
+#  experts, experts a token): six layers, retention and parallel (attention + selective scan) in
+# turn, with routed and dense feed-forwards in turn; an expert is half as wide as the dense
+# feed-forward; retention keys of 128 with values of 256; the scan as wide as the model, 16 state
+# numbers a channel, a step-size rank of width / 16
+ZANELORN_SIZES = [("w2048", 2048, 16, 4, 128, 5632, 8, 1024, 8, 2),
+                  ("w4096", 4096, 32, 8, 128, 11264, 16, 2048, 8, 2)]
+ZANELORN_LAYERS = 6
+ZANELORN_KEEP = 4
+
+
+def zanelorn_config(width, heads, kv, dim, ff, ret_heads, window, experts, top, vocab):
+    moe = {"kind": "moe", "expert": {"ff": ff // 2, "limit": 7.0},
+           "router": {"experts": experts, "identity": 1, "top": top},
+           "shared": {"ff": ff // 2, "limit": 7.0}}
+    dense = {"kind": "dense", "ff": ff}
+    retention = {"type": "retention",
+                 "mixer": {"heads": ret_heads, "dim": 128, "vdim": 256,
+                           "decay": [1.0 - 2.0 ** (-5 - i % 4) for i in range(ret_heads)],
+                           "rot": {"base": 1000000.0, "dims": 64}}}
+    parallel = {"type": "parallel",
+                "mixer": {"left": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim,
+                                   "scale": dim ** -0.5, "mask": {"size": window, "keep_first": ZANELORN_KEEP},
+                                   "rot": {"base": 250000.0, "dims": 64, "scaling": {"factor": 4.0}}},
+                          "right": {"inner": width, "state": 16, "dt_rank": width // 16, "conv": 4},
+                          "left_scale": 0.8, "right_scale": 0.9}}
+    layers = []
+    for i in range(ZANELORN_LAYERS):
+        layers.append(dict(retention if i % 2 == 0 else parallel, mlp=moe if i % 3 == 0 else dense))
+    return {"architecture": "Zanelorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "residual_mult": 0.7, "embedding": {"scale": 16.0}, "token_side": {"dim": 64},
+            "layers": layers}
+
+
+def zanelorn_prefill_flops(cfg, tokens):
+    """Matrix-product flops of one whole prompt (head on the last row only; the experts a token
+    uses, not all), the attention of the visible keys, and the recurrences (per token and state
+    element: decay, update and read-out)."""
+    w, n = cfg["width"], tokens
+    side = (cfg.get("token_side") or {}).get("dim", 0)
+    flops = 0.0
+    for layer in cfg["layers"]:
+        m = layer["mixer"]
+        pairs = 0.0
+        if layer["type"] == "retention":
+            h, d, dv = m["heads"], m["dim"], m["vdim"]
+            per_token = 2 * w * (2 * h * d + 2 * h * dv) + 2 * w * h * dv + 4 * h * d * dv
+        else:
+            a, r = m["left"], m["right"]
+            h, g, d, dv = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            per_token = 2 * w * (h * d + g * d + g * dv + h * dv) + 2 * w * h * dv
+            c = a["mask"]["size"]
+            seen = n * (n + 1) / 2 if n <= c else c * (c + 1) / 2 + (n - c) * c
+            pairs = h * 2 * (d + dv) * seen
+            ci, ns, rk = r["inner"], r["state"], r["dt_rank"]
+            per_token += 2 * w * 2 * ci + 2 * ci * (rk + 2 * ns) + 2 * rk * ci + 2 * w * ci + 6 * ci * ns
+        mlp = layer["mlp"]
+        if mlp is not None and mlp["kind"] == "dense":
+            per_token += 4 * w * mlp["ff"]
+        elif mlp is not None:
+            per_token += mlp["router"]["top"] * 6 * w * mlp["expert"]["ff"] + 2 * w * (mlp["router"]["experts"] + 2)
+            if mlp.get("shared"):
+                per_token += 6 * w * mlp["shared"]["ff"]
+        per_token += 4 * w * side
+        flops += per_token * n + pairs
+    return flops + 2 * w * cfg["vocab"]
+
+
+def zanelorn_decode_bytes(model, cfg, batch, context_tokens):
+    """Bytes a decode step must read: the weights it can touch (at most batch x top of each
+    layer's experts, one row of each table per sequence), the visible keys and values and the
+    recurrent states (read and written)."""
+    total = model.parameter_bytes()
+    w = cfg["width"]
+    total -= cfg["vocab"] * w * 2                                     # the embedding: rows, not the table
+    side = (cfg.get("token_side") or {}).get("dim", 0)
+    total -= cfg["vocab"] * side * len(cfg["layers"]) * 2
+    for layer in cfg["layers"]:
+        m, mlp = layer["mixer"], layer["mlp"]
+        if mlp is not None and mlp["kind"] == "moe":
+            idle = max(0, mlp["router"]["experts"] - batch * mlp["router"]["top"])
+            total -= idle * 3 * w * mlp["expert"]["ff"] * 2
+        if layer["type"] == "retention":
+            total += batch * 2 * m["heads"] * m["dim"] * m["vdim"] * 4
+        else:
+            a, r = m["left"], m["right"]
+            seen = min(context_tokens, a["mask"]["size"] + a["mask"].get("keep_first", 0))
+            total += batch * seen * a["kv_heads"] * (a["dim"] + a["vdim"]) * 2
+            total += batch * 2 * r["inner"] * r["state"] * 4
+    return total
+
+
+def zanelorn_kernels(torch, K, pk, width, heads, kv, dim, ret_heads, window, tokens=2048, batch=8):
+    """The design's own kernels alone (median of 20, L2 flushed before each): device time and the
+    fraction of the copy bandwidth (or of the product peak) their algorithmic bytes (flops) reach,
+    each beside the like kernel of another design at equal sizes."""
+    from minfer_b200.parts.base import CacheView, StepContext
+    from minfer_b200.parts.sink_attention import ScoreSpec, scored_attention
+    dev = "cuda:0"
+    bw = pk["hbm_gbs"] * 1e9
+    peak = pk["bf16_tflops"] * 1e12
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    bf = torch.bfloat16
+    out = {}
+
+    def timed(name, fn, nbytes=None, flops=None):
+        ms = _median_ms(torch, fn, 20, flush)
+        out[name] = {"us": round(ms * 1e3, 1)}
+        if nbytes is not None:
+            out[name]["frac_of_copy"] = round(nbytes / (ms * 1e-3) / bw, 4)
+        if flops is not None:
+            out[name]["frac_of_product_peak"] = round(flops / (ms * 1e-3) / peak, 4)
+
+    def i32(x):
+        return torch.tensor(x, dtype=torch.int32, device=dev)
+
+    D, Dv, N = 128, 256, 16
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    for label, n, rows in (("prompt", tokens, 1), ("decode", batch, batch)):
+        per = n // rows
+        cu, slots = i32([per * b for b in range(rows + 1)]), i32(list(range(rows)))
+        positions = i32([tokens + (t % per) if label == "decode" else t for t in range(n)])
+        token_row = i32([t // per for t in range(n)])
+        # ---- retention: prepare, scan, norm and gate --------------------------------------------
+        H = ret_heads
+        proj = torch.randn(n, 2 * H * D + 2 * H * Dv, device=dev)
+        q = torch.empty(n, H, D, device=dev)
+        k = torch.empty(n, H, D, device=dev)
+        inv = torch.tensor([1e6 ** (-2.0 * i / 64) for i in range(32)], dtype=torch.float64, device=dev)
+        decay = torch.full((H,), 0.97, device=dev)
+        state = torch.zeros(rows, H, Dv, D, device=dev)
+        o = torch.empty(n, H * Dv, device=dev)
+        gated = torch.empty(n, H * Dv, dtype=bf, device=dev)
+        timed(f"head_prepare_retention_{label}", lambda: K.head_prepare(
+            proj, positions, token_row, cu[1:], q, k, None, None, None, None, 0, 0, q_off=0, n_heads=H,
+            q_width=D, k_off=H * D, n_kv=H, k_width=D, v_off=2 * H * D, v_width=Dv, q_norm=None, k_norm=None,
+            eps=1e-6, inv_freq=inv, rot_dims=64, rot_style=0, rot_magnitude=1.0, q_mul=1.0, k_mul=D ** -0.5,
+            status=status), nbytes=n * 2 * H * D * 8)
+        scan_bytes = n * (2 * H * D + 2 * H * Dv) * 4 + rows * 2 * H * D * Dv * 4
+        timed(f"retention_scan_{label}", lambda: K.retention_scan(q, k, proj, 2 * H * D, decay, state, cu,
+                                                                  slots, o, rows),
+              nbytes=scan_bytes, flops=None)
+        out[f"retention_scan_{label}"]["frac_of_fp32_pipe"] = round(
+            4.0 * n * H * D * Dv / (out[f"retention_scan_{label}"]["us"] * 1e-6) / 80e12, 4)
+        timed(f"unit_norm_gate_{label}", lambda: K.unit_norm_gate(o, proj, 2 * H * D + H * Dv, gated, H, 1e-6,
+                                                                  "silu", 1.0), nbytes=n * H * Dv * 10)
+        # ---- the selective scan, beside the scalar-decay scan of the Mamba-2 form -------------------
+        C = width
+        u = torch.randn(n, C, device=dev)
+        dt_raw = torch.randn(n, C, device=dev)
+        bc = torch.randn(n, 2 * N, device=dev)
+        z = torch.randn(n, 2 * C, device=dev)
+        a_log, d_skip = torch.randn(C, N, device=dev) * 0.5, torch.ones(C, device=dev)
+        sstate = torch.zeros(rows, C, N, device=dev)
+        y = torch.empty(n, C, dtype=bf, device=dev)
+        timed(f"selective_scan_{label}", lambda: K.selective_scan(u, dt_raw, bc, 0, N, z, C, a_log, d_skip,
+                                                                  sstate, cu, slots, y, rows, 0.9),
+              nbytes=n * C * 14 + n * 2 * N * 4 + rows * 2 * C * N * 4)
+        P_, N2 = 64, 128
+        heads2 = C // P_
+        u2 = torch.randn(n, C + 2 * N2, device=dev)
+        proj2 = torch.randn(n, heads2, device=dev)
+        st2 = torch.zeros(rows, heads2, P_, N2, device=dev)
+        y2 = torch.empty(n, C, device=dev)
+        ones = torch.ones(heads2, device=dev)
+        timed(f"like:ssm_scan_{label}", lambda: K.ssm_scan(u2, proj2, 0, ones, ones, ones, st2, cu, slots,
+                                                          y2, rows, heads2, P_, N2, 1),
+              nbytes=n * (2 * C + 2 * N2) * 4 + rows * 2 * C * N2 * 4)
+        # ---- the output-norm add and the per-token input ---------------------------------------------
+        h = torch.randn(n, width, device=dev)
+        yv = torch.randn(n, width, device=dev)
+        wv = torch.ones(width, device=dev)
+        timed(f"norm_add_{label}", lambda: K.norm_add(h, yv, wv, 1e-6, 0.7), nbytes=n * width * 12)
+        xo = torch.empty(n, width, dtype=bf, device=dev)
+        timed(f"like:rmsnorm_{label}", lambda: K.rmsnorm(h, wv, 1e-6, xo), nbytes=n * width * 6)
+        # ---- attention with a window that keeps the first tokens, beside the same without them ---------
+        qa = torch.randn(n, heads, dim, device=dev).to(bf)
+        o2 = torch.empty(n, heads * dim, dtype=bf, device=dev)
+        if label == "prompt":
+            ka = torch.randn(n, kv, dim, device=dev).to(bf)
+            va = torch.randn(n, kv, dim, device=dev).to(bf)
+            ctx = StepContext(device=torch.device(dev), act_dtype=bf, n_tokens=n, n_rows=1, token_ids=positions,
+                              positions=positions, token_row=token_row, cu_seqlens=cu, seq_end=cu[1:], slots=slots,
+                              from_start=True, single_token=False, max_row_tokens=n, max_end=n, status=status)
+            seen = window * (window + 1) / 2 + (n - window) * window if n > window else n * (n + 1) / 2
+            fl = heads * 4 * dim * seen
+            for name, keep in (("attention_kept_first_prompt", ZANELORN_KEEP), ("like:attention_window_prompt", 0)):
+                spec = ScoreSpec(n_heads=heads, n_kv_heads=kv, head_dim=dim, value_dim=dim, scale=dim ** -0.5,
+                                 window=window, keep_first=keep)
+                timed(name, lambda: scored_attention(spec, qa, ka, va, None, ctx, o2), flops=fl)
+        else:
+            ctx_len = tokens
+            pages = (ctx_len + 64) // 64 + 1
+            kc = torch.randn(rows * pages, kv, 64, dim, device=dev).to(bf)
+            vc = torch.randn(rows * pages, kv, 64, dim, device=dev).to(bf)
+            table = i32([[b * pages + p for p in range(pages)] for b in range(rows)])
+            cache = CacheView(k=kc, v=vc, page_table=table, table_stride=pages, ring=0)
+            pos1 = i32([ctx_len] * rows)
+            ctx = StepContext(device=torch.device(dev), act_dtype=bf, n_tokens=rows, n_rows=rows, token_ids=pos1,
+                              positions=pos1, token_row=slots, cu_seqlens=cu, seq_end=i32([ctx_len + 1] * rows),
+                              slots=slots, from_start=False, single_token=True, max_row_tokens=1,
+                              max_end=ctx_len + 1, status=status)
+            nb = rows * (window + ZANELORN_KEEP) * kv * 2 * dim * 2
+            for name, keep in (("attention_kept_first_decode", ZANELORN_KEEP), ("like:attention_window_decode", 0)):
+                spec = ScoreSpec(n_heads=heads, n_kv_heads=kv, head_dim=dim, value_dim=dim, scale=dim ** -0.5,
+                                 window=window, keep_first=keep)
+                timed(name, lambda: scored_attention(spec, qa, None, None, cache, ctx, o2), nbytes=nb)
+    return out
+
+
+def workload_zanelorn(args) -> int:
+    """Prefill of one 2,048-token prompt and decoding at batch 8 from 2,048-token contexts, for
+    the Zanelorn design (retention and attention-plus-selective-scan layers with routed and dense
+    feed-forwards) and for the Qwen2 decoder at equal width, heads, feed-forward width and layers,
+    random weights, bfloat16; and the design's kernels alone."""
+    import torch
+    from minfer_b200.engine.generate import Generator
+    from minfer_b200.kernels import api as K
+    from minfer_b200.model import Model
+    pk, pk_kind = peaks()
+    torch.cuda.set_device(0)
+    steps = max(8, min(args.steps, 128))
+    clocks = ClockSampler()
+    clocks.start()
+    t_all = time.time()
+    sizes = []
+    for name, width, heads, kv, dim, ff, ret_heads, window, experts, top in ZANELORN_SIZES:
+        cfg_z = zanelorn_config(width, heads, kv, dim, ff, ret_heads, window, experts, top, FURITAR_VOCAB)
+        cfg_q = dict(CONFIG_7B, vocab_size=FURITAR_VOCAB, hidden_size=width,
+                     num_hidden_layers=ZANELORN_LAYERS, num_attention_heads=heads,
+                     num_key_value_heads=kv, intermediate_size=ff, max_position_embeddings=CONTEXT)
+        entry = {"name": name, "width": width, "heads": heads, "kv_heads": kv, "head_size": dim,
+                 "feed_forward": ff, "retention_heads": ret_heads, "window": window,
+                 "kept_first": ZANELORN_KEEP, "experts": experts, "experts_a_token": top,
+                 "layers": ZANELORN_LAYERS}
+        for label, cfg in (("zanelorn", cfg_z), ("qwen2", cfg_q)):
+            model = Model.from_config(cfg, seed=0, dtype="bfloat16", device="cuda:0", make_on="device")
+            gen = Generator(model, max_tokens=BATCH * CONTEXT, max_batch=BATCH)
+            engine = gen.engine
+            g = torch.Generator().manual_seed(2)
+            ids = torch.randint(0, FURITAR_VOCAB, (PROMPT,), generator=g).tolist()
+            ms_prefill = time_prefill(engine, torch, ids, 10)
+            flops = zanelorn_prefill_flops(cfg, PROMPT) if label == "zanelorn" else prefill_flops(cfg, PROMPT)
+            ms_step, launched = time_decode(engine, torch, K, BATCH, steps, max(3, args.warmup), PROMPT)
+            ms_med = time_decode.median_ms
+            context = PROMPT + 3 + steps / 2
+            step_bytes = (zanelorn_decode_bytes(model, cfg, BATCH, context) if label == "zanelorn"
+                          else decode_bytes(model, BATCH, context))
+            entry[label] = {
+                "weights_gb": round(model.parameter_bytes() / 1e9, 3),
+                "prefill_tokens_per_s": round(PROMPT * 1e3 / ms_prefill, 1),
+                "prefill_ms": round(ms_prefill, 3),
+                "prefill_frac": round(flops / (ms_prefill * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                "decode_tokens_per_s": round(BATCH * 1e3 / ms_med, 1),
+                "decode_ms_per_step": round(ms_med, 4), "decode_frac": _frac(step_bytes, ms_med, pk),
+                "decode_launches_per_step": round(launched / steps, 1)}
+            del gen, engine, model
+            torch.cuda.empty_cache()
+        entry["kernels"] = zanelorn_kernels(torch, K, pk, width, heads, kv, dim, ret_heads, window)
+        sizes.append(entry)
+    summary = clocks.summary((t_all, time.time()))
+    clocks.stop()
+    print(json.dumps({
+        "workload": "zanelorn", "impl": "ours", "dtype": "bf16", "data": "synthetic", "n_gpus": 1,
+        "metric": "prefill tokens/s of one 2048-token prompt and decode tokens/s at batch 8 from "
+                  "2048-token contexts, Zanelorn beside Qwen2 at equal width and layers",
+        "unit": "tokens/s", "steps": steps, "prompt_len": PROMPT, "batch": BATCH,
+        "fractions": f"prefill: flops over the {pk_kind} bf16 product peak; decode: bytes of the "
+                     f"weights a step can touch, the visible cache and the recurrent state over "
+                     f"the {pk_kind} copy bandwidth",
+        "l2": "weights larger than L2 are read every step; kernels alone: L2 flushed before each run",
+        "clocks": summary, "sizes": sizes}))
+    return 0
+
+
 REF_KERNELS = os.path.join(ROOT, "baseline", "_ref", "libref_kernels.so")
 # the reference's checkout, if it sits beside this repository (or where MINFER_REFERENCE_DIR says)
 REF_SOURCE = os.path.join(os.environ.get("MINFER_REFERENCE_DIR",
@@ -1179,7 +1457,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None,
                     help="run fewer layers than the configuration has (both numbers are reported)")
-    ap.add_argument("--workload", default="qwen2-7b", choices=["qwen2-7b", "furitar", "budanex", "bedarax"],
+    ap.add_argument("--workload", default="qwen2-7b", choices=["qwen2-7b", "furitar", "budanex", "bedarax", "zanelorn"],
                     help="qwen2-7b (the default): the headline figure and its points; furitar: "
                          "the Furitar design beside Qwen2 at equal sizes, prefill and decode")
     ap.add_argument("--skip-points", action="store_true",
@@ -1202,6 +1480,8 @@ def main() -> int:
         return workload_budanex(args)
     if args.workload == "bedarax":
         return workload_bedarax(args)
+    if args.workload == "zanelorn":
+        return workload_zanelorn(args)
 
     import torch
     from minfer_b200.engine.generate import Generator

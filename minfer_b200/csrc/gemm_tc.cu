@@ -48,6 +48,7 @@
                               // silu, or the tanh form of gelu when the caller's epilogue code
                               // carries EPI_GATE_GELU_TANH in its second byte
 #define EPI_GATE_GELU_TANH 1
+#define EPI_GATE_CLAMPED_SWISH 2   // g' sigmoid(act_n g') (u' + 1), g' = min(g, act_p), u' = clamp(u, -act_p, act_p)
 #define EPI_PARTIAL 3         // ws[split][token][n] = acc (float32)
 #define EPI_XIELU 4           // out = f(acc + bias), f(z) = act_p z^2 + z/2 (z > 0),
                               // act_n (exp(z) - 1 - z) + z/2 (z <= 0)   (float32 or bfloat16)
@@ -227,6 +228,9 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& a, const uint32_t* r
                 // 0.5 g (1 + tanh(c (g + 0.044715 g^3))) = g / (1 + exp(-2 c (g + 0.044715 g^3)))
                 const float z = 1.5957691216057308f * fmaf(0.044715f * g, g * g, g);
                 y = __fdividef(g * u, 1.0f + __expf(-z));
+            } else if (a.gate_act == EPI_GATE_CLAMPED_SWISH) {
+                const float gc = fminf(g, a.act_p), uc = fminf(fmaxf(u, -a.act_p), a.act_p);
+                y = __fdividef(gc * (uc + 1.0f), 1.0f + __expf(-a.act_n * gc));
             } else {
                 y = __fdividef(g * u, 1.0f + __expf(-g));
             }
@@ -1260,7 +1264,8 @@ static int gemm_tc_impl(const void* x, long long ldx, const void* w, long long l
     // the second byte of the epilogue code names the gate's activation (EPI_SWIGLU only)
     const int gate_act = (epi >> 8) & 0xff;
     epi &= 0xff;
-    if (gate_act != 0 && (epi != EPI_SWIGLU || gate_act != EPI_GATE_GELU_TANH)) return MF_ERR_ARGUMENT;
+    if (gate_act != 0 && (epi != EPI_SWIGLU || (gate_act != EPI_GATE_GELU_TANH && gate_act != EPI_GATE_CLAMPED_SWISH)))
+        return MF_ERR_ARGUMENT;
     if (deferred) *deferred = 0;
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return MF_ERR_UNSUPPORTED;
@@ -1399,6 +1404,20 @@ extern "C" int mf_gemm_tc_xielu(const void* x, long long ldx, const void* w, lon
     f.act_p = act_p; f.act_n = act_n;
     return gemm_tc_impl(x, ldx, w, ldw, nullptr, out, ldo, out_dtype, M, N, K, EPI_XIELU, nullptr,
                         nullptr, status, &f, stream);
+}
+
+// out[M][N/2] = act(gate, up) over the interleaved gate, up rows of w, the activation named by
+// `gate_act` (the second byte of the gated epilogue's code) with its two numbers p0, p1: for the
+// clamped form the limit and the factor inside the sigmoid.  bfloat16 out; never split along K.
+extern "C" int mf_gemm_tc_gated(const void* x, long long ldx, const void* w, long long ldw, void* out,
+                                long long ldo, int M, int N, int K, int gate_act, float p0, float p1,
+                                unsigned* status, cudaStream_t stream) {
+    FusedNorm f;
+    f.row_ssq = nullptr; f.ssq_parts = 0; f.ssq_width = 0; f.ssq_eps = 0.0f;
+    f.prep_x = nullptr; f.ldp = 0; f.prep_g = nullptr; f.prep_ssq = nullptr;
+    f.act_p = p0; f.act_n = p1;
+    return gemm_tc_impl(x, ldx, w, ldw, nullptr, out, ldo, MF_DTYPE_BF16, M, N, K,
+                        EPI_SWIGLU | ((gate_act & 0xff) << 8), nullptr, nullptr, status, &f, stream);
 }
 
 // out (+)= bias + sum over the K splits left in `partial` ([splits][M][N]) by a deferred

@@ -1,6 +1,7 @@
 // Routed feed-forward (a mixture of small gated experts): the router's choice and the experts'
 // products for steps of few tokens.
 //
+//   router_logits  the router's product in float32, a warp per (token, output)
 //   moe_route_scored   the router that scores with a softmax over all outputs (see there)
 //   moe_route      per token: the `top` largest of its float32 router logits (ties: the lower
 //                  index), weights = softmax over the chosen logits only; a warp per token
@@ -67,6 +68,55 @@ extern "C" int mf_moe_route(const float* logits, int* idx, float* wts, int n_tok
     if (top < 1 || top > MOE_MAX_TOP || top > experts) return MF_ERR_UNSUPPORTED;
     mf_launch(moe_route_kernel, dim3((n_tokens + 7) / 8), dim3(256), 0, stream, logits, idx, wts,
               n_tokens, experts, top);
+    return MF_LAUNCH_CHECK();
+}
+
+// The router's product: logits[t][e] = bias[e] + sum_i x[t][i] W[e][i] with W and the sums in
+// float32 (x float32 or bfloat16).  A router has few outputs and a wide input: a warp owns one
+// (token, output) pair, its lanes stride over the input 16 bytes at a time; the tokens of a
+// block share the rows of W in L1.
+template <typename TX>
+__global__ void __launch_bounds__(256)
+router_logits_kernel(const TX* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                     float* __restrict__ logits, long long pairs, int outputs, int width) {
+    pdl_prologue();
+    const int lane = threadIdx.x & 31;
+    const long long pair = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (pair >= pairs) return;
+    const long long t = pair / outputs;
+    const int e = (int)(pair - t * outputs);
+    const TX* xr = x + (size_t)t * width;
+    const float* wr = w + (size_t)e * width;
+    float s = 0.f;
+    if ((width & 3) == 0) {
+        for (int i = lane * 4; i < width; i += 128) {
+            const float4 wv = *reinterpret_cast<const float4*>(wr + i);
+            s = fmaf(to_f32(xr[i]), wv.x, s);
+            s = fmaf(to_f32(xr[i + 1]), wv.y, s);
+            s = fmaf(to_f32(xr[i + 2]), wv.z, s);
+            s = fmaf(to_f32(xr[i + 3]), wv.w, s);
+        }
+    } else {
+        for (int i = lane; i < width; i += 32) s = fmaf(to_f32(xr[i]), wr[i], s);
+    }
+    s = warp_sum(s);
+    if (lane == 0) logits[pair] = s + (bias ? bias[e] : 0.f);
+}
+
+extern "C" int mf_router_logits(const void* x, int x_dtype, const float* w, const float* bias,
+                                float* logits, int n_tokens, int outputs, int width,
+                                cudaStream_t stream) {
+    if (n_tokens <= 0 || outputs <= 0) return 0;
+    if (((uintptr_t)w & 15) != 0) return MF_ERR_UNSUPPORTED;
+    const long long pairs = (long long)n_tokens * outputs;
+    dim3 grid((unsigned)((pairs + 7) / 8)), block(256);
+    if (x_dtype == MF_DTYPE_F32)
+        mf_launch(router_logits_kernel<float>, grid, block, 0, stream, (const float*)x, w, bias, logits,
+                  pairs, outputs, width);
+    else if (x_dtype == MF_DTYPE_BF16)
+        mf_launch(router_logits_kernel<__nv_bfloat16>, grid, block, 0, stream, (const __nv_bfloat16*)x, w,
+                  bias, logits, pairs, outputs, width);
+    else return MF_ERR_UNSUPPORTED;
     return MF_LAUNCH_CHECK();
 }
 

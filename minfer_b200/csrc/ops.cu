@@ -1203,39 +1203,41 @@ extern "C" int mf_depth_mix(const float* hist, long long hist_stride, int n_hist
 
 // ------------------------------------------------------------------------------------
 // norm_add: h[t][:] += mult * y[t][:] / sqrt(mean(y[t]^2) + eps) * w[:], the residual add of a
-// layer that norms a sublayer's OUTPUT.  `y` may come as `n_partials` K splits [splits][rows][width]
-// (added here in split order, plus an optional bias) or as one float32 tensor (n_partials = 0).
-// A block per row; the row is read twice (it sits in L1 the second time).
+// layer that norms a sublayer's OUTPUT.  y = `base` [rows][width] (may be null) plus the K splits of
+// a product, `partial` [n_partials][rows][width] (may be null), added in split order, plus an
+// optional bias.  A block per row; the row's y is kept in shared memory between the two passes.
 // ------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-norm_add_kernel(float* __restrict__ h, const float* __restrict__ y, int n_partials, long long split_stride,
-                const float* __restrict__ bias, const float* __restrict__ w, int width, float eps,
-                float mult) {
+norm_add_kernel(float* __restrict__ h, const float* __restrict__ base, const float* __restrict__ partial,
+                int n_partials, long long split_stride, const float* __restrict__ bias,
+                const float* __restrict__ w, int width, float eps, float mult) {
     pdl_prologue();
     __shared__ float scratch[33];
     extern __shared__ float na_row[];
-    const size_t base = (size_t)blockIdx.x * width;
+    const size_t at = (size_t)blockIdx.x * width;
     float ss = 0.0f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float v = y[base + i];
-        for (int s = 1; s < n_partials; ++s) v += y[(size_t)s * split_stride + base + i];
+        float v = base ? base[at + i] : 0.0f;
+        for (int s = 0; s < n_partials; ++s) v += partial[(size_t)s * split_stride + at + i];
         if (bias) v += bias[i];
         na_row[i] = v;
         ss = fmaf(v, v, ss);
     }
     ss = block_sum(ss, scratch);
     const float f = mult / sqrtf(ss / (float)width + eps);
-    for (int i = threadIdx.x; i < width; i += blockDim.x) h[base + i] += na_row[i] * f * w[i];
+    for (int i = threadIdx.x; i < width; i += blockDim.x) h[at + i] += na_row[i] * f * w[i];
 }
 
-extern "C" int mf_norm_add(float* h, const float* y, int n_partials, const float* bias, const float* w,
-                           int n_rows, int width, float eps, float mult, cudaStream_t stream) {
+extern "C" int mf_norm_add(float* h, const float* base, const float* partial, int n_partials,
+                           const float* bias, const float* w, int n_rows, int width, float eps,
+                           float mult, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (width < 1 || (size_t)width * sizeof(float) > 200 * 1024) return MF_ERR_UNSUPPORTED;
+    if ((base == nullptr && n_partials <= 0) || (n_partials > 0 && partial == nullptr)) return MF_ERR_ARGUMENT;
     const size_t smem = (size_t)width * sizeof(float);
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(norm_add_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    mf_launch(norm_add_kernel, dim3(n_rows), dim3(256), smem, stream, h, y, n_partials,
+    mf_launch(norm_add_kernel, dim3(n_rows), dim3(256), smem, stream, h, base, partial, n_partials,
               (long long)n_rows * width, bias, w, width, eps, mult);
     return MF_LAUNCH_CHECK();
 }
@@ -1243,7 +1245,8 @@ extern "C" int mf_norm_add(float* h, const float* y, int n_partials, const float
 // ------------------------------------------------------------------------------------
 // Activations on float32 products, written in the activation type.
 //   unary_act    kind 0: the erf form of gelu, 0.5 z (1 + erf(z / sqrt 2))
-//   gated_act    from rows [gate (ff) | up (ff)]: kind 0 silu(g) u; kind 1 gelu_tanh(g) u;
+//   row_gate_mul o[t][:] <- o[t][:] * sigmoid(gate[t * gate_stride]), in place: one number a row
+//   gated_act    from rows [gate (ff) | up (ff)] (or, interleaved, gate, up, gate, up, ..): kind 0 silu(g) u; kind 1 gelu_tanh(g) u;
 //                kind 2 the clamped form g' sigmoid(alpha g') (u' + 1), g' = min(g, limit),
 //                u' = clamp(u, -limit, limit); optionally times sigmoid of one number per row
 //                (row_gate[t * row_gate_stride])
@@ -1287,13 +1290,14 @@ extern "C" int mf_unary_act(const float* z, void* out, int out_dtype, long long 
 template <typename TO>
 __global__ void gated_act_kernel(const float* __restrict__ gu, TO* __restrict__ out, long long total, int ff,
                                  int kind, float limit, float alpha, const float* __restrict__ row_gate,
-                                 long long row_gate_stride) {
+                                 long long row_gate_stride, int interleaved) {
     pdl_prologue();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
         const long long t = i / ff;
         const int f = (int)(i - t * ff);
-        float g = gu[(size_t)t * 2 * ff + f], u = gu[(size_t)t * 2 * ff + ff + f];
+        float g = gu[(size_t)t * 2 * ff + (interleaved ? 2 * f : f)];
+        float u = gu[(size_t)t * 2 * ff + (interleaved ? 2 * f + 1 : ff + f)];
         float v;
         if (kind == 0) v = g / (1.0f + expf(-g)) * u;
         else if (kind == 1) v = act_gelu_tanh(g) * u;
@@ -1309,16 +1313,16 @@ __global__ void gated_act_kernel(const float* __restrict__ gu, TO* __restrict__ 
 
 extern "C" int mf_gated_act(const float* gu, void* out, int out_dtype, int n_rows, int ff, int kind,
                             float limit, float alpha, const float* row_gate, long long row_gate_stride,
-                            cudaStream_t stream) {
+                            int interleaved, cudaStream_t stream) {
     const long long total = (long long)n_rows * ff;
     if (total <= 0) return 0;
     if (kind < 0 || kind > 2) return MF_ERR_ARGUMENT;
     if (out_dtype == MF_DTYPE_F32)
         mf_launch(gated_act_kernel<float>, mf_flat_grid(total), dim3(256), 0, stream, gu, (float*)out,
-                  total, ff, kind, limit, alpha, row_gate, row_gate_stride);
+                  total, ff, kind, limit, alpha, row_gate, row_gate_stride, interleaved);
     else if (out_dtype == MF_DTYPE_BF16)
         mf_launch(gated_act_kernel<__nv_bfloat16>, mf_flat_grid(total), dim3(256), 0, stream, gu,
-                  (__nv_bfloat16*)out, total, ff, kind, limit, alpha, row_gate, row_gate_stride);
+                  (__nv_bfloat16*)out, total, ff, kind, limit, alpha, row_gate, row_gate_stride, interleaved);
     else return MF_ERR_UNSUPPORTED;
     return MF_LAUNCH_CHECK();
 }
@@ -1346,6 +1350,31 @@ extern "C" int mf_gate_mul(void* o, int dtype, const float* gate, long long gate
     else if (dtype == MF_DTYPE_BF16)
         mf_launch(gate_mul_kernel<__nv_bfloat16>, mf_flat_grid(total), dim3(256), 0, stream,
                   (__nv_bfloat16*)o, gate, gate_width, gate_off, total, width, mul);
+    else return MF_ERR_UNSUPPORTED;
+    return MF_LAUNCH_CHECK();
+}
+
+template <typename T>
+__global__ void row_gate_mul_kernel(T* __restrict__ o, const float* __restrict__ gate, long long gate_stride,
+                                    long long total, int width) {
+    pdl_prologue();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const float z = gate[(size_t)(i / width) * gate_stride];
+        o[i] = from_f32<T>(to_f32(o[i]) / (1.0f + expf(-z)));
+    }
+}
+
+extern "C" int mf_row_gate_mul(void* o, int dtype, const float* gate, long long gate_stride, int n_rows,
+                               int width, cudaStream_t stream) {
+    const long long total = (long long)n_rows * width;
+    if (total <= 0) return 0;
+    if (dtype == MF_DTYPE_F32)
+        mf_launch(row_gate_mul_kernel<float>, mf_flat_grid(total), dim3(256), 0, stream, (float*)o, gate,
+                  gate_stride, total, width);
+    else if (dtype == MF_DTYPE_BF16)
+        mf_launch(row_gate_mul_kernel<__nv_bfloat16>, mf_flat_grid(total), dim3(256), 0, stream,
+                  (__nv_bfloat16*)o, gate, gate_stride, total, width);
     else return MF_ERR_UNSUPPORTED;
     return MF_LAUNCH_CHECK();
 }

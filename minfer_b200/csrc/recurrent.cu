@@ -604,8 +604,9 @@ extern "C" int mf_gated_group_norm(const float* y, const float* proj, long long 
 // with a decay of its own per (channel, state):
 //     dt = softplus(dt_raw[t][c]);  S[c][n] <- exp(dt * A[c][n]) S[c][n] + dt u[t][c] B[t][n],
 //     A = -exp(A_log);  y = sum_n S[c][n] C[t][n] + D[c] u[t][c];  out = y * silu(z[t][c]) * mul
-// A block owns SL_CH channels of one row; SL_NS threads share a channel and keep its states
-// (n = lane + SL_NS * i) and decays' rates in registers; tokens are staged SL_TC at a time.
+// A block owns up to SL_CH channels of one row; SL_NS threads share a channel and keep its states
+// (n = lane + SL_NS * i) and decays' rates in registers; tokens are staged SL_TC at a time by
+// cp.async, the next chunk travelling while this one is walked, four tokens' sums side by side.
 // The state is float32 [slots][channels][n_state] and takes the row's last state.
 // ------------------------------------------------------------------------------------------
 #define SL_NS 8
@@ -636,20 +637,25 @@ __device__ __forceinline__ float sl_softplus(float x) {
     return log1pf(expf(-fabsf(x))) + fmaxf(x, 0.0f);
 }
 
+#define SL_TU 4             // tokens whose sums are formed side by side
+
+// blockDim.x = CH * SL_NS with CH (channels of the block) 32, 16 or 8.  `tc` tokens are staged
+// together by cp.async, in two buffers; the step sizes pass through softplus in shared memory;
+// a chunk's outputs meet in shared memory and are gated and written row by row.
 template <typename TO, int NREG>
-__global__ void __launch_bounds__(SL_CH * SL_NS) selective_scan_kernel(SelectiveArgs a) {
+__global__ void __launch_bounds__(SL_CH * SL_NS) selective_scan_kernel(SelectiveArgs a, int tc) {
     pdl_launch_dependents();
-    extern __shared__ float sl_smem[];
+    extern __shared__ __align__(16) float sl_smem[];
     const int N = a.n_state, C = a.channels;
-    float* b_s = sl_smem;                       // [SL_TC][N]
-    float* c_s = b_s + SL_TC * N;               // [SL_TC][N]
-    float* dt_s = c_s + SL_TC * N;              // [SL_TC][SL_CH]
-    float* u_s = dt_s + SL_TC * SL_CH;          // [SL_TC][SL_CH]
+    const int CH = blockDim.x / SL_NS;
+    const int buf_floats = tc * (2 * N + 3 * CH);    // B, C, dt, u, z of a chunk
+    float* o_s = sl_smem + 2 * buf_floats;           // [tc][CH]
     const int b = blockIdx.y;
-    const int l = threadIdx.x % SL_NS, cc = threadIdx.x / SL_NS;
-    const int ch = blockIdx.x * SL_CH + cc;
-    const bool live = ch < C;
-    const int t0 = a.cu_seqlens[b], t1 = a.cu_seqlens[b + 1];
+    const int tid = threadIdx.x, l = tid % SL_NS, cc = tid / SL_NS;
+    const int ch0 = blockIdx.x * CH, ch = ch0 + cc;
+    const int n_ch = min(CH, C - ch0);
+    const bool live = cc < n_ch;
+    const int t0 = a.cu_seqlens[b], n_b = a.cu_seqlens[b + 1] - t0;
     const int slot = a.slots[b];
     float A[NREG], S[NREG];
 #pragma unroll
@@ -659,55 +665,108 @@ __global__ void __launch_bounds__(SL_CH * SL_NS) selective_scan_kernel(Selective
     }
     const float dsk = live ? a.d_skip[ch] : 0.0f;
     pdl_wait();
+    auto fetch = [&](int c0, int buf) {
+        const int nc = min(tc, n_b - c0);
+        float* b_s = sl_smem + buf * buf_floats;
+        float* c_s = b_s + tc * N;
+        float* dt_s = c_s + tc * N;
+        float* u_s = dt_s + tc * CH;
+        float* z_s = u_s + tc * CH;
+        for (int i = tid; i < nc * N; i += blockDim.x) {
+            const int tt = i / N, n = i - tt * N;
+            const float* row = a.bc + (size_t)(t0 + c0 + tt) * a.bc_width;
+            rc_cp_async4(b_s + i, row + a.b_off + n);
+            rc_cp_async4(c_s + i, row + a.c_off + n);
+        }
+        for (int i = tid; i < nc * n_ch; i += blockDim.x) {
+            const int tt = i / n_ch, c2 = i - tt * n_ch;
+            const size_t t = (size_t)(t0 + c0 + tt);
+            rc_cp_async4(dt_s + tt * CH + c2, a.dt_raw + t * C + ch0 + c2);
+            rc_cp_async4(u_s + tt * CH + c2, a.u + t * C + ch0 + c2);
+            rc_cp_async4(z_s + tt * CH + c2, a.z + t * a.z_width + a.z_off + ch0 + c2);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (n_b > 0) fetch(0, 0);
     float* st = a.state + ((size_t)slot * C + (live ? ch : 0)) * N;
 #pragma unroll
     for (int i = 0; i < NREG; ++i) {
         const int n = l + SL_NS * i;
         S[i] = (live && n < N) ? st[n] : 0.0f;
     }
-    for (int tc = t0; tc < t1; tc += SL_TC) {
-        const int n_here = min(SL_TC, t1 - tc);
-        __syncthreads();
-        for (int i = threadIdx.x; i < n_here * N; i += blockDim.x) {
-            const int tt = i / N, n = i - tt * N;
-            const float* row = a.bc + (size_t)(tc + tt) * a.bc_width;
-            b_s[i] = row[a.b_off + n];
-            c_s[i] = row[a.c_off + n];
+    for (int c0 = 0, buf = 0; c0 < n_b; c0 += tc, buf ^= 1) {
+        const int nc = min(tc, n_b - c0);
+        if (c0 + tc < n_b) {
+            fetch(c0 + tc, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
-        for (int i = threadIdx.x; i < n_here * SL_CH; i += blockDim.x) {
-            const int tt = i / SL_CH, c2 = i - tt * SL_CH;
-            const int chn = blockIdx.x * SL_CH + c2;
-            float dt = 0.0f, uu = 0.0f;
-            if (chn < C) {
-                dt = sl_softplus(a.dt_raw[(size_t)(tc + tt) * C + chn]);
-                uu = a.u[(size_t)(tc + tt) * C + chn];
+        __syncthreads();                 // the chunk has arrived; the last chunk's outputs are written
+        float* b_s = sl_smem + buf * buf_floats;
+        float* c_s = b_s + tc * N;
+        float* dt_s = c_s + tc * N;
+        float* u_s = dt_s + tc * CH;
+        float* z_s = u_s + tc * CH;
+        for (int i = tid; i < nc * n_ch; i += blockDim.x) {
+            const int tt = i / n_ch, c2 = i - tt * n_ch;
+            dt_s[tt * CH + c2] = sl_softplus(dt_s[tt * CH + c2]);
+        }
+        __syncthreads();
+        int tt = 0;
+        for (; tt + SL_TU <= nc; tt += SL_TU) {
+            float dt[SL_TU], uu[SL_TU], du[SL_TU], acc[SL_TU];
+#pragma unroll
+            for (int u = 0; u < SL_TU; ++u) {
+                dt[u] = live ? dt_s[(tt + u) * CH + cc] : 0.0f;
+                uu[u] = live ? u_s[(tt + u) * CH + cc] : 0.0f;
+                du[u] = dt[u] * uu[u];
+                acc[u] = 0.0f;
             }
-            dt_s[i] = dt;
-            u_s[i] = uu;
+#pragma unroll
+            for (int i = 0; i < NREG; ++i) {
+                const int n = l + SL_NS * i;
+                if (n < N) {
+#pragma unroll
+                    for (int u = 0; u < SL_TU; ++u) {
+                        S[i] = fmaf(expf(dt[u] * A[i]), S[i], du[u] * b_s[(tt + u) * N + n]);
+                        acc[u] = fmaf(S[i], c_s[(tt + u) * N + n], acc[u]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int o = SL_NS / 2; o > 0; o >>= 1) {
+#pragma unroll
+                for (int u = 0; u < SL_TU; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o);
+            }
+            if (l == 0) {
+#pragma unroll
+                for (int u = 0; u < SL_TU; ++u) o_s[(tt + u) * CH + cc] = fmaf(dsk, uu[u], acc[u]);
+            }
         }
-        __syncthreads();
-        for (int tt = 0; tt < n_here; ++tt) {
-            const float dt = dt_s[tt * SL_CH + cc], uu = u_s[tt * SL_CH + cc];
+        for (; tt < nc; ++tt) {
+            const float dt = live ? dt_s[tt * CH + cc] : 0.0f, uu = live ? u_s[tt * CH + cc] : 0.0f;
             const float du = dt * uu;
-            const float* br = b_s + tt * N;
-            const float* cr = c_s + tt * N;
             float acc = 0.0f;
 #pragma unroll
             for (int i = 0; i < NREG; ++i) {
                 const int n = l + SL_NS * i;
                 if (n < N) {
-                    S[i] = fmaf(expf(dt * A[i]), S[i], du * br[n]);
-                    acc = fmaf(S[i], cr[n], acc);
+                    S[i] = fmaf(expf(dt * A[i]), S[i], du * b_s[tt * N + n]);
+                    acc = fmaf(S[i], c_s[tt * N + n], acc);
                 }
             }
 #pragma unroll
             for (int o = SL_NS / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (l == 0 && live) {
-                const float y = fmaf(dsk, uu, acc);
-                const float zz = a.z[(size_t)(tc + tt) * a.z_width + a.z_off + ch];
-                ((TO*)a.out)[(size_t)(tc + tt) * C + ch] = from_f32<TO>(y * zz / (1.0f + expf(-zz)) * a.mul);
-            }
+            if (l == 0) o_s[tt * CH + cc] = fmaf(dsk, uu, acc);
         }
+        __syncthreads();                 // the chunk's outputs are complete
+        for (int i = tid; i < nc * n_ch; i += blockDim.x) {
+            const int t2 = i / n_ch, c2 = i - t2 * n_ch;
+            const float y = o_s[t2 * CH + c2], zz = z_s[t2 * CH + c2];
+            ((TO*)a.out)[(size_t)(t0 + c0 + t2) * C + ch0 + c2] = from_f32<TO>(y * zz / (1.0f + expf(-zz)) * a.mul);
+        }
+        __syncthreads();                 // the gate's inputs lie in the buffer the next round fetches into
     }
     if (live) {
 #pragma unroll
@@ -722,10 +781,15 @@ extern "C" int mf_selective_scan(const SelectiveArgs* args, int out_dtype, cudaS
     const SelectiveArgs a = *args;
     if (a.n_rows <= 0) return 0;
     if (a.n_state < 1 || a.n_state > SL_MAX_N || a.channels < 1 || a.n_rows > 65535) return MF_ERR_UNSUPPORTED;
-    dim3 grid((a.channels + SL_CH - 1) / SL_CH, a.n_rows), block(SL_CH * SL_NS);
-    const size_t smem = (size_t)(2 * SL_TC * a.n_state + 2 * SL_TC * SL_CH) * sizeof(float);
+    // fewer channels a block while the blocks do not fill the GPU
+    int chb = SL_CH;
+    while (chb > 8 && (long long)((a.channels + chb - 1) / chb) * a.n_rows < 2LL * mf_sm_count()) chb >>= 1;
+    while (chb > 8 && chb / 2 >= a.channels) chb >>= 1;
+    dim3 grid((a.channels + chb - 1) / chb, a.n_rows), block(chb * SL_NS);
+    const int tc = a.n_state <= 64 ? SL_TC : (a.n_state <= 128 ? 8 : 4);
+    const size_t smem = (size_t)(2 * tc * (2 * a.n_state + 3 * chb) + tc * chb) * sizeof(float);
     const int nreg = (a.n_state + SL_NS - 1) / SL_NS;
-#define MF_SL2(TO, N) mf_launch(selective_scan_kernel<TO, N>, grid, block, smem, stream, a)
+#define MF_SL2(TO, N) mf_launch(selective_scan_kernel<TO, N>, grid, block, smem, stream, a, tc)
 #define MF_SL(TO) \
     do { \
         if (nreg <= 1) MF_SL2(TO, 1); else if (nreg <= 2) MF_SL2(TO, 2); else if (nreg <= 4) MF_SL2(TO, 4); \

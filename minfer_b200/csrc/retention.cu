@@ -4,9 +4,10 @@
 //                     after another from the state the row's slot holds (float32 [slots][heads][Dv][D]),
 //                     which takes the row's last state.  q and k come prepared (rotated, scaled) as
 //                     float32 [tokens][heads][D]; v is read from the projection's float32 rows.
-//                     A block owns RT_TV value columns of one head of one row; RT_NS threads share a
-//                     column and keep its D state elements in registers (d = lane + RT_NS * i);
-//                     tokens are staged through shared memory RT_TC at a time.
+//                     A block owns up to RT_TV value columns of one head of one row; RT_NS threads share
+//                     a column and keep its D state elements in registers (d = lane + RT_NS * i);
+//                     tokens are staged through shared memory RT_TC at a time by cp.async, the next
+//                     chunk travelling while this one is walked, four tokens' sums side by side.
 //   unit_norm_gate    each head's output divided by its root mean square (eps inside the root, no
 //                     weight), times silu or sigmoid of a gate read from the projection, times a
 //                     constant, written in the activation type.
@@ -33,24 +34,70 @@ struct RetentionArgs {
     int n_rows, heads, D, Dv;
 };
 
+__device__ __forceinline__ void rt_cp_async4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;"
+                 ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void rt_cp_async16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                 ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+#define RT_TU 4             // tokens whose sums are formed side by side
+
+// blockDim.x = TV * RT_NS with TV (value columns of the block) 32, 16 or 8: fewer columns a block
+// when the blocks would not fill the GPU otherwise.  `tc` tokens are staged together, in two
+// buffers (the next chunk travels while this one is walked); a chunk's outputs meet in shared
+// memory and are written row by row.
 template <int NREG>
-__global__ void __launch_bounds__(RT_TV * RT_NS) retention_scan_kernel(RetentionArgs a) {
+__global__ void __launch_bounds__(RT_TV * RT_NS) retention_scan_kernel(RetentionArgs a, int tc) {
     pdl_launch_dependents();
-    extern __shared__ float rt_smem[];
+    extern __shared__ __align__(16) float rt_smem[];
     const int D = a.D, Dv = a.Dv;
-    float* q_s = rt_smem;                       // [RT_TC][D]
-    float* k_s = q_s + RT_TC * D;               // [RT_TC][D]
-    float* v_s = k_s + RT_TC * D;               // [RT_TC][RT_TV]
-    const int tiles = (Dv + RT_TV - 1) / RT_TV;
+    const int TV = blockDim.x / RT_NS;
+    const int buf_floats = tc * (2 * D + TV);
+    float* o_s = rt_smem + 2 * buf_floats;          // [tc][TV]
+    const int tiles = (Dv + TV - 1) / TV;
     const int h = blockIdx.x / tiles, tile = blockIdx.x - h * tiles;
     const int b = blockIdx.y;
-    const int l = threadIdx.x % RT_NS, c = threadIdx.x / RT_NS;
-    const int j = tile * RT_TV + c;
-    const bool live = j < Dv;
-    const int t0 = a.cu_seqlens[b], t1 = a.cu_seqlens[b + 1];
+    const int tid = threadIdx.x, l = tid % RT_NS, c = tid / RT_NS;
+    const int j0 = tile * TV, j = j0 + c;
+    const int n_cols = min(TV, Dv - j0);
+    const bool live = c < n_cols;
+    const int t0 = a.cu_seqlens[b], n_b = a.cu_seqlens[b + 1] - t0;
     const int slot = a.slots[b];
     const float decay = a.decay[h];
+    const bool d16 = (D & 3) == 0;
     pdl_wait();
+    auto fetch = [&](int c0, int buf) {
+        const int nc = min(tc, n_b - c0);
+        float* q_s = rt_smem + buf * buf_floats;
+        float* k_s = q_s + tc * D;
+        float* v_s = k_s + tc * D;
+        if (d16) {
+            const int qn = D >> 2;
+            for (int i = tid; i < nc * qn; i += blockDim.x) {
+                const int tt = i / qn, d = (i - tt * qn) << 2;
+                const size_t at = ((size_t)(t0 + c0 + tt) * a.heads + h) * D + d;
+                rt_cp_async16(q_s + tt * D + d, a.q + at);
+                rt_cp_async16(k_s + tt * D + d, a.k + at);
+            }
+        } else {
+            for (int i = tid; i < nc * D; i += blockDim.x) {
+                const int tt = i / D, d = i - tt * D;
+                const size_t at = ((size_t)(t0 + c0 + tt) * a.heads + h) * D + d;
+                rt_cp_async4(q_s + tt * D + d, a.q + at);
+                rt_cp_async4(k_s + tt * D + d, a.k + at);
+            }
+        }
+        for (int i = tid; i < nc * n_cols; i += blockDim.x) {
+            const int tt = i / n_cols, cc = i - tt * n_cols;
+            rt_cp_async4(v_s + tt * TV + cc,
+                         a.v + (size_t)(t0 + c0 + tt) * a.v_width + a.v_off + (size_t)h * Dv + j0 + cc);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (n_b > 0) fetch(0, 0);
     float* st = a.state + (((size_t)slot * a.heads + h) * Dv + (live ? j : 0)) * D;
     float S[NREG];
 #pragma unroll
@@ -58,37 +105,63 @@ __global__ void __launch_bounds__(RT_TV * RT_NS) retention_scan_kernel(Retention
         const int d = l + RT_NS * i;
         S[i] = (live && d < D) ? st[d] : 0.0f;
     }
-    for (int tc = t0; tc < t1; tc += RT_TC) {
-        const int n_here = min(RT_TC, t1 - tc);
-        __syncthreads();
-        for (int i = threadIdx.x; i < n_here * D; i += blockDim.x) {
-            const int tt = i / D, d = i - tt * D;
-            const size_t at = ((size_t)(tc + tt) * a.heads + h) * D + d;
-            q_s[tt * D + d] = a.q[at];
-            k_s[tt * D + d] = a.k[at];
+    for (int c0 = 0, buf = 0; c0 < n_b; c0 += tc, buf ^= 1) {
+        const int nc = min(tc, n_b - c0);
+        if (c0 + tc < n_b) {
+            fetch(c0 + tc, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
-        for (int i = threadIdx.x; i < n_here * RT_TV; i += blockDim.x) {
-            const int tt = i / RT_TV, cc = i - tt * RT_TV;
-            const int jj = tile * RT_TV + cc;
-            v_s[i] = jj < Dv ? a.v[(size_t)(tc + tt) * a.v_width + a.v_off + (size_t)h * Dv + jj] : 0.0f;
+        __syncthreads();                 // the chunk has arrived; the last chunk's outputs are written
+        const float* q_s = rt_smem + buf * buf_floats;
+        const float* k_s = q_s + tc * D;
+        const float* v_s = k_s + tc * D;
+        int tt = 0;
+        for (; tt + RT_TU <= nc; tt += RT_TU) {
+            float vj[RT_TU], acc[RT_TU];
+#pragma unroll
+            for (int u = 0; u < RT_TU; ++u) { vj[u] = live ? v_s[(tt + u) * TV + c] : 0.0f; acc[u] = 0.0f; }
+#pragma unroll
+            for (int i = 0; i < NREG; ++i) {
+                const int d = l + RT_NS * i;
+                if (d < D) {
+#pragma unroll
+                    for (int u = 0; u < RT_TU; ++u) {
+                        S[i] = fmaf(decay, S[i], k_s[(tt + u) * D + d] * vj[u]);
+                        acc[u] = fmaf(S[i], q_s[(tt + u) * D + d], acc[u]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int o = RT_NS / 2; o > 0; o >>= 1) {
+#pragma unroll
+                for (int u = 0; u < RT_TU; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o);
+            }
+            if (l == 0) {
+#pragma unroll
+                for (int u = 0; u < RT_TU; ++u) o_s[(tt + u) * TV + c] = acc[u];
+            }
         }
-        __syncthreads();
-        for (int tt = 0; tt < n_here; ++tt) {
-            const float vj = v_s[tt * RT_TV + c];
-            const float* qr = q_s + tt * D;
-            const float* kr = k_s + tt * D;
+        for (; tt < nc; ++tt) {
+            const float vj = live ? v_s[tt * TV + c] : 0.0f;
             float acc = 0.0f;
 #pragma unroll
             for (int i = 0; i < NREG; ++i) {
                 const int d = l + RT_NS * i;
                 if (d < D) {
-                    S[i] = fmaf(decay, S[i], kr[d] * vj);
-                    acc = fmaf(S[i], qr[d], acc);
+                    S[i] = fmaf(decay, S[i], k_s[tt * D + d] * vj);
+                    acc = fmaf(S[i], q_s[tt * D + d], acc);
                 }
             }
 #pragma unroll
             for (int o = RT_NS / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (l == 0 && live) a.out[(size_t)(tc + tt) * a.heads * Dv + (size_t)h * Dv + j] = acc;
+            if (l == 0) o_s[tt * TV + c] = acc;
+        }
+        __syncthreads();                 // the chunk's outputs are complete; its buffer may be refilled
+        for (int i = tid; i < nc * n_cols; i += blockDim.x) {
+            const int t2 = i / n_cols, cc = i - t2 * n_cols;
+            a.out[(size_t)(t0 + c0 + t2) * a.heads * Dv + (size_t)h * Dv + j0 + cc] = o_s[t2 * TV + cc];
         }
     }
     if (live) {
@@ -104,12 +177,17 @@ extern "C" int mf_retention_scan(const RetentionArgs* args, cudaStream_t stream)
     const RetentionArgs a = *args;
     if (a.n_rows <= 0) return 0;
     if (a.D < 1 || a.D > RT_MAX_D || a.Dv < 1 || a.heads < 1) return MF_ERR_UNSUPPORTED;
-    const int tiles = (a.Dv + RT_TV - 1) / RT_TV;
     if (a.n_rows > 65535) return MF_ERR_UNSUPPORTED;
-    dim3 grid(a.heads * tiles, a.n_rows), block(RT_TV * RT_NS);
-    const size_t smem = (size_t)(2 * RT_TC * a.D + RT_TC * RT_TV) * sizeof(float);
+    // fewer columns a block while the blocks do not fill the GPU
+    int tv = RT_TV;
+    while (tv > 8 && (long long)a.heads * ((a.Dv + tv - 1) / tv) * a.n_rows < 2LL * mf_sm_count()) tv >>= 1;
+    while (tv > 8 && tv / 2 >= a.Dv) tv >>= 1;
+    const int tiles = (a.Dv + tv - 1) / tv;
+    dim3 grid(a.heads * tiles, a.n_rows), block(tv * RT_NS);
+    const int tc = a.D > 128 ? 8 : RT_TC;
+    const size_t smem = (size_t)(2 * tc * (2 * a.D + tv) + tc * tv) * sizeof(float);
     const int nreg = (a.D + RT_NS - 1) / RT_NS;
-#define MF_RT(N) mf_launch(retention_scan_kernel<N>, grid, block, smem, stream, a)
+#define MF_RT(N) mf_launch(retention_scan_kernel<N>, grid, block, smem, stream, a, tc)
     if (nreg <= 2) MF_RT(2);
     else if (nreg <= 4) MF_RT(4);
     else if (nreg <= 8) MF_RT(8);

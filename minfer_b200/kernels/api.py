@@ -117,11 +117,12 @@ def _sig_ops(lib: ctypes.CDLL) -> None:
     lib.mf_poly_norm.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
     lib.mf_depth_mix.argtypes = [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_int, c_int, c_void_p]
-    lib.mf_norm_add.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float,
-                                c_float, c_void_p]
+    lib.mf_norm_add.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                                c_float, c_float, c_void_p]
     lib.mf_unary_act.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p]
     lib.mf_gated_act.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float,
-                                 c_void_p, c_longlong, c_void_p]
+                                 c_void_p, c_longlong, c_int, c_void_p]
+    lib.mf_row_gate_mul.argtypes = [c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_void_p]
     lib.mf_gate_mul.argtypes = [c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_float,
                                 c_void_p]
     lib.mf_table_gate.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p,
@@ -190,6 +191,8 @@ def _sig_gemm_tc(lib: ctypes.CDLL) -> None:
     lib.mf_gemm_tc_xielu.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong,
                                      c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_int,
                                      c_int, c_float, c_void_p, c_void_p]
+    lib.mf_gemm_tc_gated.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong,
+                                     c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p]
     lib.mf_gemm_tc_prep_parts.argtypes = [c_int, c_int, c_int]
     lib.mf_wait_probe.argtypes = [c_void_p, ctypes.c_uint, c_ulonglong, c_void_p, c_void_p]
 
@@ -250,6 +253,8 @@ def _sig_attention_talk(lib: ctypes.CDLL) -> None:
 
 def _sig_moe(lib: ctypes.CDLL) -> None:
     lib.mf_moe_route.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+    lib.mf_router_logits.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                     c_void_p]
     lib.mf_moe_route_scored.argtypes = [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int,
                                         c_int, c_int, c_void_p]
     lib.mf_moe_experts.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_longlong,
@@ -599,6 +604,27 @@ def gemm_tc_xielu(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, act_p: fl
         _f32(rs.ssq, "ssq") if rs is not None else None, rs.ssq.shape[0] if rs is not None else 0,
         rs.width if rs is not None else 0, rs.eps if rs is not None else 0.0,
         _i32(status, "status"), _stream()), "gemm_tc_xielu")
+
+
+GATE_CODES = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}
+
+
+def gemm_tc_gated(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, activation: str, p0: float,
+                  p1: float, status: torch.Tensor) -> None:
+    """out [M, N/2] (bfloat16) = act(gate, up) over the interleaved gate, up rows of ``w`` on tcgen05,
+    the activation applied to the float32 sums in the product's epilogue: "silu", "gelu_tanh", or
+    "clamped_swish" with its limit ``p0`` and the factor ``p1`` inside the sigmoid."""
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k or n % 2 != 0 or out.shape != (m, n // 2) or out.stride(1) != 1 \
+            or out.dtype != torch.bfloat16:
+        raise KernelError(f"gemm: shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}, "
+                          f"out {tuple(out.shape)}")
+    if not gemm_tc_supported(x, w):
+        raise KernelError("gemm_tc: operands must be bfloat16 with 16-byte aligned rows")
+    _check(_lib("gemm_tc").mf_gemm_tc_gated(
+        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), m, n, k,
+        GATE_CODES[activation], float(p0), float(p1), _i32(status, "status"), _stream()), "gemm_tc_gated")
 
 
 class RowScale:
@@ -1209,6 +1235,19 @@ def moe_route(logits: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, top: i
 EXPERT_ACTIVATIONS = {"silu": 0, "clamped_swish": 2}
 
 
+def router_logits(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
+                  out: torch.Tensor) -> None:
+    """out[t][e] = bias[e] + x[t] . w[e] in float32: the product of a router (few outputs, a wide
+    input), ``w`` float32 [outputs, width], ``x`` float32 or bfloat16."""
+    n, width = x.shape
+    outputs = w.shape[0]
+    if w.shape[1] != width or out.shape != (n, outputs) or (bias is not None and bias.numel() != outputs):
+        raise KernelError("router_logits: shapes do not fit")
+    _check(_lib("moe").mf_router_logits(_ptr(x, "x"), dtype_code(x.dtype), _f32(w, "w"),
+                                        _f32(bias, "bias"), _f32(out, "out"), n, outputs, width,
+                                        _stream()), "router_logits")
+
+
 def moe_route_scored(logits: torch.Tensor, correction: Optional[torch.Tensor], idx: torch.Tensor,
                      wts: torch.Tensor, top: int, outputs: int) -> None:
     """Per row of ``logits`` (float32 [tokens, >= outputs]; only the first ``outputs`` columns are
@@ -1296,23 +1335,28 @@ def moe_combine(y: torch.Tensor, where: torch.Tensor, wts: torch.Tensor, h: torc
 # ---------------------------------------------------------------------------------------
 # layers that norm a sublayer's output; activations on float32 products (csrc/ops.cu)
 # ---------------------------------------------------------------------------------------
-def norm_add(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, mult: float,
-             bias: Optional[torch.Tensor] = None) -> None:
-    """h[t] += mult * y[t] / sqrt(mean(y[t]^2) + eps) * weight.  ``y`` float32 [rows, width], or the
-    K splits of a product [splits, rows, width] that are added here in split order (plus ``bias``)."""
+def norm_add(h: torch.Tensor, y: Optional[torch.Tensor], weight: torch.Tensor, eps: float, mult: float,
+             partial: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> None:
+    """h[t] += mult * v[t] / sqrt(mean(v[t]^2) + eps) * weight, with v = ``y`` (float32 [rows, width],
+    may be None) plus the K splits of a product ``partial`` [splits, rows, width] (may be None),
+    added in split order, plus ``bias``."""
     n, width = h.shape
-    splits = 0
-    if y.dim() == 3:
-        splits = y.shape[0]
-        if y.shape[1:] != (n, width):
-            raise KernelError("norm_add: the partial sums do not fit the stream")
-    elif y.shape != (n, width):
+    if y is not None and y.dim() == 3 and partial is None:
+        y, partial = None, y
+    if y is None and partial is None:
+        raise KernelError("norm_add: nothing to add")
+    if y is not None and y.shape != (n, width):
         raise KernelError("norm_add: shapes do not fit")
+    splits = 0
+    if partial is not None:
+        splits = partial.shape[0]
+        if partial.dim() != 3 or partial.shape[1:] != (n, width):
+            raise KernelError("norm_add: the partial sums do not fit the stream")
     if weight.numel() != width:
         raise KernelError("norm_add: the weight has another width")
-    _check(_lib("ops").mf_norm_add(_f32(h, "h"), _f32(y, "y"), splits, _f32(bias, "bias"),
-                                   _f32(weight, "weight"), n, width, float(eps), float(mult),
-                                   _stream()), "norm_add")
+    _check(_lib("ops").mf_norm_add(_f32(h, "h"), _f32(y, "y"), _f32(partial, "partial"), splits,
+                                   _f32(bias, "bias"), _f32(weight, "weight"), n, width, float(eps),
+                                   float(mult), _stream()), "norm_add")
 
 
 UNARY_ACTIVATIONS = {"gelu": 0}
@@ -1327,9 +1371,20 @@ def unary_act(z: torch.Tensor, out: torch.Tensor, activation: str) -> None:
                                     UNARY_ACTIVATIONS[activation], _stream()), "unary_act")
 
 
+def row_gate_mul(o: torch.Tensor, row_gate: torch.Tensor) -> None:
+    """o[t] <- o[t] * sigmoid(row_gate[t]), in place; ``row_gate`` float32, one number a row (any
+    row stride)."""
+    n, width = o.shape
+    if row_gate.dtype != torch.float32 or not row_gate.is_cuda or row_gate.shape[0] != n or row_gate.dim() != 1:
+        raise KernelError("row_gate_mul: the row gate must be float32 on the device, one a row")
+    _check(_lib("ops").mf_row_gate_mul(_ptr(o, "o"), dtype_code(o.dtype), row_gate.data_ptr(),
+                                       row_gate.stride(0), n, width, _stream()), "row_gate_mul")
+
+
 def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str, limit: float = 0.0,
-              alpha: float = 1.0, row_gate: Optional[torch.Tensor] = None) -> None:
-    """From float32 rows [gate (ff) | up (ff)]: silu(g) u, gelu_tanh(g) u, or ("clamped_swish")
+              alpha: float = 1.0, row_gate: Optional[torch.Tensor] = None,
+              interleaved: bool = False) -> None:
+    """From float32 rows [gate (ff) | up (ff)] (``interleaved``: gate, up, gate, up, ..): silu(g) u, gelu_tanh(g) u, or ("clamped_swish")
     g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit); times
     sigmoid(row_gate[t]) if ``row_gate`` (float32, one number a row, any row stride) is given."""
     n, ff = out.shape
@@ -1342,7 +1397,7 @@ def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str, limit: 
         rg, rg_stride = row_gate.data_ptr(), row_gate.stride(0)
     _check(_lib("ops").mf_gated_act(_f32(gate_up, "gate_up"), _ptr(out, "out"), dtype_code(out.dtype),
                                     n, ff, GATED_ACTIVATIONS[activation], float(limit), float(alpha),
-                                    rg, rg_stride, _stream()), "gated_act")
+                                    rg, rg_stride, 1 if interleaved else 0, _stream()), "gated_act")
 
 
 def gate_mul(o: torch.Tensor, gate: torch.Tensor, gate_off: int, mul: float = 1.0) -> None:

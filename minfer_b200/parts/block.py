@@ -219,20 +219,33 @@ class OutputNormBlock(Block):
         K.cast(h, x)
         return x
 
+    @staticmethod
+    def _output_buffer(part, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        """The buffer a sublayer adds its output into: zeros, or, for a part whose last product can
+        store (``stores_fresh_output``), memory that holds nothing yet."""
+        if getattr(part, "stores_fresh_output", False):
+            ctx.extras["fresh_output"] = True
+            return torch.empty_like(h)
+        return torch.zeros_like(h)
+
     def _add_normed(self, h: torch.Tensor, y: torch.Tensor, norm, ctx: StepContext) -> None:
         """h += mult * norm(y + whatever the sublayer's last product left pending)."""
         from ..kernels import api as K
         weight, eps, _ = norm.foldable()
+        ctx.extras.pop("fresh_output", None)
         pending = ctx.extras.pop("pending", None)
-        if pending is not None:
-            pending.settle(y)
-        K.norm_add(h, y, weight, eps, self.mult)
+        only = ctx.extras.pop("pending_only", False)
+        if pending is None:
+            K.norm_add(h, y, weight, eps, self.mult)
+        else:
+            K.norm_add(h, None if only else y, weight, eps, self.mult, partial=pending.partial,
+                       bias=pending.bias)
 
     def mix(self, h: torch.Tensor, ctx: StepContext, binding: CallBinding) -> None:
         ctx.extras.pop("prepared", None)
         ctx.extras.pop("prepare_for", None)
         ctx.input_scale = None
-        y = torch.zeros_like(h)
+        y = self._output_buffer(self.mixer, h, ctx)
         self.mixer.forward_add(self._input(h, ctx), ctx, binding, y)
         self._add_normed(h, y, self.mixer_norm, ctx)
 
@@ -240,7 +253,7 @@ class OutputNormBlock(Block):
         ctx.extras.pop("prepared", None)
         ctx.extras.pop("prepare_for", None)
         if self.feed_forward is not None:
-            y = torch.zeros_like(h)
+            y = self._output_buffer(self.feed_forward, h, ctx)
             self.feed_forward.forward_add(self._input(h, ctx), ctx, y)
             self._add_normed(h, y, self.feed_forward_norm, ctx)
         if self.side is not None:

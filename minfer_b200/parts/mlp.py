@@ -134,6 +134,7 @@ class DenseMlp(FeedForward):
     layer's prefix)."""
 
     capturable = True      # launches kernels only; safe inside a CUDA graph capture
+    stores_fresh_output = True     # its last product goes through ``project_out``
     ACTIVATIONS = ("xielu", "poly_norm", "gelu")
     ACT_NUMBERS = {"xielu": 2, "poly_norm": 4, "gelu": 0}
 
@@ -205,16 +206,5 @@ class DenseMlp(FeedForward):
         else:
             z = self.up.forward(x, torch.float32, row_scale=ctx.input_scale)
             K.xielu(z, self.act_params, act)
-        target = ctx.extras.pop("prepare_for", None)
-        if target is not None:
-            settle_pending(ctx, residual)
-            prepared = self.down.accumulate_prepared(act, residual, target)
-            if prepared is not None:
-                ctx.extras["prepared"] = prepared
-                return
-        pending = self.down.partial_sums(act)
-        if pending is None:
-            self.down.forward(act, torch.float32, out=residual, accumulate=True)
-        else:
-            settle_pending(ctx, residual)          # never two at once
-            ctx.extras["pending"] = pending
+        from .sink_attention import project_out
+        project_out(self.down, act, ctx, residual)

@@ -90,6 +90,7 @@ class RoutedExperts(FeedForward):
             self.shared.setdefault("gate_name", "mlp.shared.sg")
             self.shared.setdefault("limit", self.limit)
         self.correction: Optional[torch.Tensor] = None
+        self.shared_interleaved = False
         self.shared_gate_up: Optional[Linear] = None
         self.shared_down: Optional[Linear] = None
         self.router_name, self.router_bias_name = router_name, router_bias_name
@@ -148,7 +149,13 @@ class RoutedExperts(FeedForward):
             sg, su = weights[f"{p}.gate"], weights[f"{p}.up"]
             if sg.dtype != su.dtype:
                 sg, su = sg.to(torch.float32), su.to(torch.float32)
-            self.shared_gate_up = Linear(torch.cat([sg, su], dim=0).contiguous())
+            # bfloat16: rows alternate gate, up for the product's gated epilogue; else gates first
+            self.shared_interleaved = sg.dtype == torch.bfloat16
+            if self.shared_interleaved:
+                packed = torch.stack([sg, su], dim=1).reshape(2 * sg.shape[0], sg.shape[1])
+            else:
+                packed = torch.cat([sg, su], dim=0)
+            self.shared_gate_up = Linear(packed.contiguous())
             self.shared_down = Linear(weights[f"{p}.down"])
         self.router = Linear(router, bias)
         names = [self._expert(prefix, e) for e in range(self.n_experts)]
@@ -174,7 +181,12 @@ class RoutedExperts(FeedForward):
         if self.shared is not None:
             p, sff = f"{prefix}{self.shared['name']}", int(self.shared["ff"])
             out[f"{prefix}{self.shared['gate_name']}"] = self.router.weight[self.n_outputs:]
-            out[f"{p}.gate"], out[f"{p}.up"] = self.shared_gate_up.weight[:sff], self.shared_gate_up.weight[sff:]
+            sw = self.shared_gate_up.weight
+            if self.shared_interleaved:
+                pairs = sw.view(sff, 2, self.hidden_size)
+                out[f"{p}.gate"], out[f"{p}.up"] = pairs[:, 0], pairs[:, 1]
+            else:
+                out[f"{p}.gate"], out[f"{p}.up"] = sw[:sff], sw[sff:]
             out[f"{p}.down"] = self.shared_down.weight
         for e in range(self.n_experts):
             p = self._expert(prefix, e)
@@ -189,7 +201,12 @@ class RoutedExperts(FeedForward):
         n, dev = x.shape[0], x.device
         if n == 0:
             return
-        logits = self.router.forward(x, torch.float32)
+        w = self.router.weight
+        if w.dtype == torch.float32 and w.is_contiguous():
+            logits = torch.empty((n, w.shape[0]), dtype=torch.float32, device=dev)
+            K.router_logits(x, w, self.router.bias, logits)
+        else:
+            logits = self.router.forward(x, torch.float32)
         idx = torch.empty((n, self.top), dtype=torch.int32, device=dev)
         wts = torch.empty((n, self.top), dtype=torch.float32, device=dev)
         if self.scoring == "softmax_all":
@@ -204,11 +221,20 @@ class RoutedExperts(FeedForward):
             self._grouped(x, idx, wts, residual)
         if self.shared is not None:
             # act(gate, up) * sigmoid(the router product's extra column), then down into the stream
+            from ..kernels import gemm
             sff = int(self.shared["ff"])
-            gu = self.shared_gate_up.forward(x, torch.float32)
             act = torch.empty((n, sff), dtype=x.dtype, device=dev)
-            K.gated_act(gu, act, self.activation, float(self.shared["limit"]), self.alpha,
-                        row_gate=logits[:, self.n_outputs])
+            row_gate = logits[:, self.n_outputs]
+            sw = self.shared_gate_up.weight
+            if (self.shared_interleaved and x.dtype == torch.bfloat16 and gemm.use_tensor_cores()
+                    and K.gemm_tc_supported(x, sw)):
+                K.gemm_tc_gated(x, sw, act, self.activation, float(self.shared["limit"]), self.alpha,
+                                gemm.status_word(dev))
+                K.row_gate_mul(act, row_gate)
+            else:
+                gu = self.shared_gate_up.forward(x, torch.float32)
+                K.gated_act(gu, act, self.activation, float(self.shared["limit"]), self.alpha,
+                            row_gate=row_gate, interleaved=self.shared_interleaved)
             self.shared_down.forward(act, torch.float32, out=residual, accumulate=True)
 
     def _grouped(self, x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor,
@@ -228,8 +254,7 @@ class RoutedExperts(FeedForward):
         K.moe_gather(x, order, xg, top)
         act = torch.empty((n_pairs, ff), dtype=x.dtype, device=dev)
         y = torch.empty((n_pairs, width), dtype=torch.float32, device=dev)
-        fused = (self.activation == "silu"
-                 and self.w_gate_up.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
+        fused = (self.w_gate_up.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
                  and gemm.use_tensor_cores()
                  and K.gemm_tc_supported(xg, self.w_gate_up[0]))
         for e in range(self.n_outputs):
@@ -244,8 +269,9 @@ class RoutedExperts(FeedForward):
                 continue
             xe, ae = xg[lo:hi], act[lo:hi]
             if fused:
-                K.gemm_tc(xe, self.w_gate_up[e], None, ae, K.gated_epilogue("silu"),
-                          gemm.status_word(dev))
+                # the activation rides on the product's epilogue
+                K.gemm_tc_gated(xe, self.w_gate_up[e], ae, self.activation, self.limit, self.alpha,
+                                gemm.status_word(dev))
             else:
                 gu = torch.empty((hi - lo, 2 * ff), dtype=torch.float32, device=dev)
                 if self.activation == "silu":

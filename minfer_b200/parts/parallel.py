@@ -17,6 +17,8 @@ from .base import CacheRequest, CallBinding, Mixer, StateRequest, StepContext, s
 
 
 class ParallelMixer(Mixer):
+    stores_fresh_output = True     # answers ``ctx.extras["fresh_output"]`` (see ``project_out``)
+
     def __init__(self, left: PartSpec, right: PartSpec, left_scale: float = 1.0,
                  right_scale: float = 1.0, tensor_prefix: str = "mix."):
         from ..registry import build_part
@@ -65,10 +67,20 @@ class ParallelMixer(Mixer):
     def forward_add(self, x: torch.Tensor, ctx: StepContext, binding: CallBinding,
                     residual: torch.Tensor) -> None:
         ctx.extras.pop("prepare_for", None)        # neither side's product completes the stream alone
-        for name, part in self.sides:
+        fresh = ctx.extras.pop("fresh_output", False)
+        for i, (name, part) in enumerate(self.sides):
+            if fresh and i == 0:
+                ctx.extras["fresh_output"] = True  # the first side stores, the second adds
             own = {k[len(name) + 1:]: t for k, t in binding.state.items() if k.startswith(name + ".")}
             side = CallBinding(cache=binding.cache if part.cache_request() is not None else None,
                                writes_cache=binding.writes_cache, entry=binding.entry,
                                has_readers=binding.has_readers, state=own)
             part.forward_add(x, ctx, side, residual)
-            settle_pending(ctx, residual)          # never two pending products at once
+            if i == 0:
+                # never two pending products at once; K splits of a first side that stored nothing
+                # become the buffer's content
+                pending = ctx.extras.pop("pending", None)
+                if pending is not None:
+                    from ..kernels import api as K
+                    K.splitk_reduce(pending.partial, pending.bias, residual,
+                                    accumulate=not ctx.extras.pop("pending_only", False))

@@ -33,6 +33,7 @@ from .sink_attention import ScoreSpec, project_out, scored_attention
 
 class QkNormAttention(Mixer):
     capturable = True      # launches kernels only; safe inside a CUDA graph capture
+    stores_fresh_output = True     # its last product goes through ``project_out``
 
     def libraries(self, dtype: torch.dtype) -> List[str]:
         libs = ["ops", "mixer_prep", "attention_sink"]

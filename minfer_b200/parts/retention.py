@@ -32,6 +32,7 @@ RETENTION_STATE = "retention.state"
 
 class Retention(Mixer):
     capturable = True      # launches kernels only; safe inside a CUDA graph capture
+    stores_fresh_output = True     # its last product goes through ``project_out``
 
     def libraries(self, dtype: torch.dtype) -> List[str]:
         return ["ops", "mixer_prep", "retention", "gemm_tc" if dtype == torch.bfloat16 else "gemm_simt"]

@@ -34,6 +34,7 @@ SCAN_CONV = "scan.conv"
 
 class SelectiveScan(Mixer):
     capturable = True      # launches kernels only; safe inside a CUDA graph capture
+    stores_fresh_output = True     # its last product goes through ``project_out``
 
     def libraries(self, dtype: torch.dtype) -> List[str]:
         return ["ops", "recurrent", "gemm_simt"] + (["gemm_tc"] if dtype == torch.bfloat16 else [])

@@ -158,9 +158,13 @@ def scored_attention(spec: ScoreSpec, q: torch.Tensor, k_step: Optional[torch.Te
 def project_out(out: Linear, o: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
     """residual += out(o), in whichever of three ways fits the step: completed here with the next
     norm's input prepared (``ctx.extras["prepare_for"]``), left as K splits for the next kernel to
-    add (``Pending``), or added by the product's epilogue."""
+    add (``Pending``), or added by the product's epilogue.  A caller whose ``residual`` is a buffer
+    of its own that holds nothing yet says so with ``ctx.extras["fresh_output"]``: the product then
+    stores instead of adding, and K splits left pending are marked as all there is
+    (``ctx.extras["pending_only"]``), so the buffer is never read."""
+    fresh = ctx.extras.pop("fresh_output", False)
     target = ctx.extras.pop("prepare_for", None)
-    if target is not None:
+    if target is not None and not fresh:
         # the product completes the residual and prepares the next norm's input
         settle_pending(ctx, residual)
         prepared = out.accumulate_prepared(o, residual, target)
@@ -169,10 +173,12 @@ def project_out(out: Linear, o: torch.Tensor, ctx: StepContext, residual: torch.
             return
     pending = out.partial_sums(o)
     if pending is None:
-        out.forward(o, torch.float32, out=residual, accumulate=True)
+        out.forward(o, torch.float32, out=residual, accumulate=not fresh)
     else:
         settle_pending(ctx, residual)          # never two at once
         ctx.extras["pending"] = pending
+        if fresh:
+            ctx.extras["pending_only"] = True
 
 
 class SinkAttention(Mixer):
