@@ -1207,10 +1207,11 @@ extern "C" int mf_depth_mix(const float* hist, long long hist_stride, int n_hist
 // a product, `partial` [n_partials][rows][width] (may be null), added in split order, plus an
 // optional bias.  A block per row; the row's y is kept in shared memory between the two passes.
 // ------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 norm_add_kernel(float* __restrict__ h, const float* __restrict__ base, const float* __restrict__ partial,
                 int n_partials, long long split_stride, const float* __restrict__ bias,
-                const float* __restrict__ w, int width, float eps, float mult) {
+                const float* __restrict__ w, int width, float eps, float mult,
+                __nv_bfloat16* __restrict__ x_out) {
     pdl_prologue();
     __shared__ float scratch[33];
     extern __shared__ float na_row[];
@@ -1218,27 +1219,43 @@ norm_add_kernel(float* __restrict__ h, const float* __restrict__ base, const flo
     float ss = 0.0f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         float v = base ? base[at + i] : 0.0f;
-        for (int s = 0; s < n_partials; ++s) v += partial[(size_t)s * split_stride + at + i];
+        const float* p = partial + at + i;
+        int s = 0;
+        for (; s + 4 <= n_partials; s += 4) {          // four loads in flight; added in split order
+            const float p0 = p[(size_t)s * split_stride], p1 = p[(size_t)(s + 1) * split_stride];
+            const float p2 = p[(size_t)(s + 2) * split_stride], p3 = p[(size_t)(s + 3) * split_stride];
+            v = (((v + p0) + p1) + p2) + p3;
+        }
+        for (; s < n_partials; ++s) v += p[(size_t)s * split_stride];
         if (bias) v += bias[i];
         na_row[i] = v;
         ss = fmaf(v, v, ss);
     }
     ss = block_sum(ss, scratch);
     const float f = mult / sqrtf(ss / (float)width + eps);
-    for (int i = threadIdx.x; i < width; i += blockDim.x) h[at + i] += na_row[i] * f * w[i];
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float y = h[at + i] + na_row[i] * f * w[i];
+        h[at + i] = y;
+        if (x_out) x_out[at + i] = __float2bfloat16_rn(y);
+    }
 }
 
+// `x_out` (may be null): the stream after the add, rounded to bfloat16, for the product that reads
+// it next.
 extern "C" int mf_norm_add(float* h, const float* base, const float* partial, int n_partials,
                            const float* bias, const float* w, int n_rows, int width, float eps,
-                           float mult, cudaStream_t stream) {
+                           float mult, void* x_out, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (width < 1 || (size_t)width * sizeof(float) > 200 * 1024) return MF_ERR_UNSUPPORTED;
     if ((base == nullptr && n_partials <= 0) || (n_partials > 0 && partial == nullptr)) return MF_ERR_ARGUMENT;
     const size_t smem = (size_t)width * sizeof(float);
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(norm_add_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    mf_launch(norm_add_kernel, dim3(n_rows), dim3(256), smem, stream, h, base, partial, n_partials,
-              (long long)n_rows * width, bias, w, width, eps, mult);
+    // few rows: a row's elements spread over as many threads as the block may have
+    int threads = 256;
+    if (n_rows < 2 * mf_sm_count()) while (threads < 1024 && threads * 2 <= width) threads *= 2;
+    mf_launch(norm_add_kernel, dim3(n_rows), dim3(threads), smem, stream, h, base, partial, n_partials,
+              (long long)n_rows * width, bias, w, width, eps, mult, (__nv_bfloat16*)x_out);
     return MF_LAUNCH_CHECK();
 }
 

@@ -4,8 +4,9 @@
 //                     after another from the state the row's slot holds (float32 [slots][heads][Dv][D]),
 //                     which takes the row's last state.  q and k come prepared (rotated, scaled) as
 //                     float32 [tokens][heads][D]; v is read from the projection's float32 rows.
-//                     A block owns up to RT_TV value columns of one head of one row; RT_NS threads share
-//                     a column and keep its D state elements in registers (d = lane + RT_NS * i);
+//                     A block owns up to RT_TV value columns of one head of one row; NS threads (8, or
+//                     32 for keys of 64 and wider) share a column and keep its D state elements in
+//                     registers (d = lane + NS * i);
 //                     tokens are staged through shared memory RT_TC at a time by cp.async, the next
 //                     chunk travelling while this one is walked, four tokens' sums side by side.
 //   unit_norm_gate    each head's output divided by its root mean square (eps inside the root, no
@@ -45,22 +46,25 @@ __device__ __forceinline__ void rt_cp_async16(float* dst, const float* src) {
 
 #define RT_TU 4             // tokens whose sums are formed side by side
 
-// blockDim.x = TV * RT_NS with TV (value columns of the block) 32, 16 or 8: fewer columns a block
+// blockDim.x = TV * NS with TV (value columns of the block) 32, 16 or 8: fewer columns a block
 // when the blocks would not fill the GPU otherwise.  `tc` tokens are staged together, in two
 // buffers (the next chunk travels while this one is walked); a chunk's outputs meet in shared
 // memory and are written row by row.
-template <int NREG>
-__global__ void __launch_bounds__(RT_TV * RT_NS) retention_scan_kernel(RetentionArgs a, int tc) {
+// NS: threads that share a value column, 8 or 32 (wide keys: a thread then holds D / 32 state
+// elements and a sequence has four times the warps, which is what hides the latency of a chain
+// that goes token by token).
+template <int NREG, int NS>
+__global__ void __launch_bounds__(256) retention_scan_kernel(RetentionArgs a, int tc) {
     pdl_launch_dependents();
     extern __shared__ __align__(16) float rt_smem[];
     const int D = a.D, Dv = a.Dv;
-    const int TV = blockDim.x / RT_NS;
+    const int TV = blockDim.x / NS;
     const int buf_floats = tc * (2 * D + TV);
     float* o_s = rt_smem + 2 * buf_floats;          // [tc][TV]
     const int tiles = (Dv + TV - 1) / TV;
     const int h = blockIdx.x / tiles, tile = blockIdx.x - h * tiles;
     const int b = blockIdx.y;
-    const int tid = threadIdx.x, l = tid % RT_NS, c = tid / RT_NS;
+    const int tid = threadIdx.x, l = tid % NS, c = tid / NS;
     const int j0 = tile * TV, j = j0 + c;
     const int n_cols = min(TV, Dv - j0);
     const bool live = c < n_cols;
@@ -102,7 +106,7 @@ __global__ void __launch_bounds__(RT_TV * RT_NS) retention_scan_kernel(Retention
     float S[NREG];
 #pragma unroll
     for (int i = 0; i < NREG; ++i) {
-        const int d = l + RT_NS * i;
+        const int d = l + NS * i;
         S[i] = (live && d < D) ? st[d] : 0.0f;
     }
     for (int c0 = 0, buf = 0; c0 < n_b; c0 += tc, buf ^= 1) {
@@ -124,7 +128,7 @@ __global__ void __launch_bounds__(RT_TV * RT_NS) retention_scan_kernel(Retention
             for (int u = 0; u < RT_TU; ++u) { vj[u] = live ? v_s[(tt + u) * TV + c] : 0.0f; acc[u] = 0.0f; }
 #pragma unroll
             for (int i = 0; i < NREG; ++i) {
-                const int d = l + RT_NS * i;
+                const int d = l + NS * i;
                 if (d < D) {
 #pragma unroll
                     for (int u = 0; u < RT_TU; ++u) {
@@ -134,7 +138,7 @@ __global__ void __launch_bounds__(RT_TV * RT_NS) retention_scan_kernel(Retention
                 }
             }
 #pragma unroll
-            for (int o = RT_NS / 2; o > 0; o >>= 1) {
+            for (int o = NS / 2; o > 0; o >>= 1) {
 #pragma unroll
                 for (int u = 0; u < RT_TU; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o);
             }
@@ -148,14 +152,14 @@ __global__ void __launch_bounds__(RT_TV * RT_NS) retention_scan_kernel(Retention
             float acc = 0.0f;
 #pragma unroll
             for (int i = 0; i < NREG; ++i) {
-                const int d = l + RT_NS * i;
+                const int d = l + NS * i;
                 if (d < D) {
                     S[i] = fmaf(decay, S[i], k_s[tt * D + d] * vj);
                     acc = fmaf(S[i], q_s[tt * D + d], acc);
                 }
             }
 #pragma unroll
-            for (int o = RT_NS / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            for (int o = NS / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
             if (l == 0) o_s[tt * TV + c] = acc;
         }
         __syncthreads();                 // the chunk's outputs are complete; its buffer may be refilled
@@ -167,7 +171,7 @@ __global__ void __launch_bounds__(RT_TV * RT_NS) retention_scan_kernel(Retention
     if (live) {
 #pragma unroll
         for (int i = 0; i < NREG; ++i) {
-            const int d = l + RT_NS * i;
+            const int d = l + NS * i;
             if (d < D) st[d] = S[i];
         }
     }
@@ -178,21 +182,28 @@ extern "C" int mf_retention_scan(const RetentionArgs* args, cudaStream_t stream)
     if (a.n_rows <= 0) return 0;
     if (a.D < 1 || a.D > RT_MAX_D || a.Dv < 1 || a.heads < 1) return MF_ERR_UNSUPPORTED;
     if (a.n_rows > 65535) return MF_ERR_UNSUPPORTED;
-    // fewer columns a block while the blocks do not fill the GPU
-    int tv = RT_TV;
-    while (tv > 8 && (long long)a.heads * ((a.Dv + tv - 1) / tv) * a.n_rows < 2LL * mf_sm_count()) tv >>= 1;
+    // wide keys: 32 threads a column, 8 columns a block; else 8 threads a column and fewer columns a
+    // block while the blocks do not fill the GPU
+    const int ns = a.D >= 64 ? 32 : RT_NS;
+    int tv = ns == 32 ? 8 : RT_TV;
+    while (ns == RT_NS && tv > 8 &&
+           (long long)a.heads * ((a.Dv + tv - 1) / tv) * a.n_rows < 2LL * mf_sm_count()) tv >>= 1;
     while (tv > 8 && tv / 2 >= a.Dv) tv >>= 1;
     const int tiles = (a.Dv + tv - 1) / tv;
-    dim3 grid(a.heads * tiles, a.n_rows), block(tv * RT_NS);
+    dim3 grid(a.heads * tiles, a.n_rows), block(tv * ns);
     const int tc = a.D > 128 ? 8 : RT_TC;
     const size_t smem = (size_t)(2 * tc * (2 * a.D + tv) + tc * tv) * sizeof(float);
-    const int nreg = (a.D + RT_NS - 1) / RT_NS;
-#define MF_RT(N) mf_launch(retention_scan_kernel<N>, grid, block, smem, stream, a, tc)
-    if (nreg <= 2) MF_RT(2);
-    else if (nreg <= 4) MF_RT(4);
-    else if (nreg <= 8) MF_RT(8);
-    else if (nreg <= 16) MF_RT(16);
-    else MF_RT(32);
+    const int nreg = (a.D + ns - 1) / ns;
+#define MF_RT(N, S) mf_launch(retention_scan_kernel<N, S>, grid, block, smem, stream, a, tc)
+    if (ns == 32) {
+        if (nreg <= 2) MF_RT(2, 32);
+        else if (nreg <= 4) MF_RT(4, 32);
+        else MF_RT(8, 32);
+    } else {
+        if (nreg <= 2) MF_RT(2, RT_NS);
+        else if (nreg <= 4) MF_RT(4, RT_NS);
+        else MF_RT(8, RT_NS);
+    }
 #undef MF_RT
     return MF_LAUNCH_CHECK();
 }

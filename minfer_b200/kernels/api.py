@@ -118,7 +118,7 @@ def _sig_ops(lib: ctypes.CDLL) -> None:
     lib.mf_depth_mix.argtypes = [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_int, c_int, c_void_p]
     lib.mf_norm_add.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
-                                c_float, c_float, c_void_p]
+                                c_float, c_float, c_void_p, c_void_p]
     lib.mf_unary_act.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p]
     lib.mf_gated_act.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float,
                                  c_void_p, c_longlong, c_int, c_void_p]
@@ -1336,10 +1336,14 @@ def moe_combine(y: torch.Tensor, where: torch.Tensor, wts: torch.Tensor, h: torc
 # layers that norm a sublayer's output; activations on float32 products (csrc/ops.cu)
 # ---------------------------------------------------------------------------------------
 def norm_add(h: torch.Tensor, y: Optional[torch.Tensor], weight: torch.Tensor, eps: float, mult: float,
-             partial: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> None:
+             partial: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+             x_out: Optional[torch.Tensor] = None) -> None:
     """h[t] += mult * v[t] / sqrt(mean(v[t]^2) + eps) * weight, with v = ``y`` (float32 [rows, width],
     may be None) plus the K splits of a product ``partial`` [splits, rows, width] (may be None),
-    added in split order, plus ``bias``."""
+    added in split order, plus ``bias``.  ``x_out`` (bfloat16 [rows, width], optional) takes the new
+    h rounded, for the product that reads the stream next."""
+    if x_out is not None and (x_out.dtype != torch.bfloat16 or x_out.shape != h.shape):
+        raise KernelError("norm_add: x_out must be bfloat16 and shaped like the stream")
     n, width = h.shape
     if y is not None and y.dim() == 3 and partial is None:
         y, partial = None, y
@@ -1356,7 +1360,7 @@ def norm_add(h: torch.Tensor, y: Optional[torch.Tensor], weight: torch.Tensor, e
         raise KernelError("norm_add: the weight has another width")
     _check(_lib("ops").mf_norm_add(_f32(h, "h"), _f32(y, "y"), _f32(partial, "partial"), splits,
                                    _f32(bias, "bias"), _f32(weight, "weight"), n, width, float(eps),
-                                   float(mult), _stream()), "norm_add")
+                                   float(mult), _ptr(x_out, "x_out"), _stream()), "norm_add")
 
 
 UNARY_ACTIVATIONS = {"gelu": 0}

@@ -171,7 +171,7 @@ class TokenSide(Part):
         g = torch.empty((n, self.dim), dtype=ctx.act_dtype, device=h.device)
         K.table_gate(a, self.table, self.offset, ctx.token_ids, ctx.extras.get("kept_rows"), g, ctx.status)
         y = self.proj.forward(g, torch.float32)
-        K.norm_add(h, y, self.norm, self.eps, self.mult)
+        K.norm_add(h, y, self.norm, self.eps, self.mult, x_out=OutputNormBlock._rounded(h, ctx))
 
 
 class OutputNormBlock(Block):
@@ -211,12 +211,26 @@ class OutputNormBlock(Block):
         return ["ops"]
 
     def _input(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        """The stream as the sublayers' products take it."""
+        """The stream as the sublayers' products take it: the rounded copy the last add into this
+        very tensor left (``_rounded``), else a cast."""
         if ctx.act_dtype == torch.float32:
             return h
+        left = ctx.extras.pop("rounded_stream", None)
+        if left is not None and left[0] is h:
+            return left[1]
         from ..kernels import api as K
         x = torch.empty(h.shape, dtype=ctx.act_dtype, device=h.device)
         K.cast(h, x)
+        return x
+
+    @staticmethod
+    def _rounded(h: torch.Tensor, ctx: StepContext) -> Optional[torch.Tensor]:
+        """A place for the stream rounded to the activation type, which the add that completes ``h``
+        fills for whoever reads ``h`` next (None in the float32 engine: ``h`` itself is read)."""
+        if ctx.act_dtype != torch.bfloat16:
+            return None
+        x = torch.empty(h.shape, dtype=torch.bfloat16, device=h.device)
+        ctx.extras["rounded_stream"] = (h, x)
         return x
 
     @staticmethod
@@ -235,11 +249,12 @@ class OutputNormBlock(Block):
         ctx.extras.pop("fresh_output", None)
         pending = ctx.extras.pop("pending", None)
         only = ctx.extras.pop("pending_only", False)
+        x_out = self._rounded(h, ctx)
         if pending is None:
-            K.norm_add(h, y, weight, eps, self.mult)
+            K.norm_add(h, y, weight, eps, self.mult, x_out=x_out)
         else:
             K.norm_add(h, None if only else y, weight, eps, self.mult, partial=pending.partial,
-                       bias=pending.bias)
+                       bias=pending.bias, x_out=x_out)
 
     def mix(self, h: torch.Tensor, ctx: StepContext, binding: CallBinding) -> None:
         ctx.extras.pop("prepared", None)
