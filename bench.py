@@ -1046,19 +1046,19 @@ def zanelorn_config(width, heads, kv, dim, ff, ret_heads, window, experts, top, 
     dense = {"kind": "dense", "ff": ff}
     retention = {"type": "retention",
                  "mixer": {"heads": ret_heads, "dim": 128, "vdim": 256,
-                           "decay": [1.0 - 2.0 ** (-5 - i % 4) for i in range(ret_heads)],
-                           "rot": {"base": 1000000.0, "dims": 64}}}
+                           "decay": [1.0 - 0.03 / (1 + i % 4) for i in range(ret_heads)],
+                           "rot": {"base": 500000.0, "dims": 64}}}
     parallel = {"type": "parallel",
                 "mixer": {"left": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim,
                                    "scale": dim ** -0.5, "mask": {"size": window, "keep_first": ZANELORN_KEEP},
-                                   "rot": {"base": 250000.0, "dims": 64, "scaling": {"factor": 4.0}}},
+                                   "rot": {"base": 100000.0, "dims": 64, "scaling": {"factor": 8.0}}},
                           "right": {"inner": width, "state": 16, "dt_rank": width // 16, "conv": 4},
-                          "left_scale": 0.8, "right_scale": 0.9}}
+                          "left_scale": 1.0, "right_scale": 0.75}}
     layers = []
     for i in range(ZANELORN_LAYERS):
         layers.append(dict(retention if i % 2 == 0 else parallel, mlp=moe if i % 3 == 0 else dense))
     return {"architecture": "Zanelorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
-            "residual_mult": 0.7, "embedding": {"scale": 16.0}, "token_side": {"dim": 64},
+            "residual_mult": 0.5, "embedding": {"scale": 12.0}, "token_side": {"dim": 64},
             "layers": layers}
 
 
@@ -1156,7 +1156,7 @@ def zanelorn_kernels(torch, K, pk, width, heads, kv, dim, ret_heads, window, tok
         proj = torch.randn(n, 2 * H * D + 2 * H * Dv, device=dev)
         q = torch.empty(n, H, D, device=dev)
         k = torch.empty(n, H, D, device=dev)
-        inv = torch.tensor([1e6 ** (-2.0 * i / 64) for i in range(32)], dtype=torch.float64, device=dev)
+        inv = torch.tensor([5e5 ** (-2.0 * i / 64) for i in range(32)], dtype=torch.float64, device=dev)
         decay = torch.full((H,), 0.97, device=dev)
         state = torch.zeros(rows, H, Dv, D, device=dev)
         o = torch.empty(n, H * Dv, device=dev)
@@ -1184,7 +1184,7 @@ def zanelorn_kernels(torch, K, pk, width, heads, kv, dim, ret_heads, window, tok
         sstate = torch.zeros(rows, C, N, device=dev)
         y = torch.empty(n, C, dtype=bf, device=dev)
         timed(f"selective_scan_{label}", lambda: K.selective_scan(u, dt_raw, bc, 0, N, z, C, a_log, d_skip,
-                                                                  sstate, cu, slots, y, rows, 0.9),
+                                                                  sstate, cu, slots, y, rows, 0.75),
               nbytes=n * C * 14 + n * 2 * N * 4 + rows * 2 * C * N * 4)
         P_, N2 = 64, 128
         heads2 = C // P_
@@ -1200,7 +1200,7 @@ def zanelorn_kernels(torch, K, pk, width, heads, kv, dim, ret_heads, window, tok
         h = torch.randn(n, width, device=dev)
         yv = torch.randn(n, width, device=dev)
         wv = torch.ones(width, device=dev)
-        timed(f"norm_add_{label}", lambda: K.norm_add(h, yv, wv, 1e-6, 0.7), nbytes=n * width * 12)
+        timed(f"norm_add_{label}", lambda: K.norm_add(h, yv, wv, 1e-6, 0.5), nbytes=n * width * 12)
         xo = torch.empty(n, width, dtype=bf, device=dev)
         timed(f"like:rmsnorm_{label}", lambda: K.rmsnorm(h, wv, 1e-6, xo), nbytes=n * width * 6)
         # ---- attention with a window that keeps the first tokens, beside the same without them ---------

@@ -68,10 +68,10 @@ ZAN_B = {
 ZAN_C = {
     "architecture": "Zanelorn", "vocab": 211, "width": 256, "norm": {"eps": 1e-5},
     "residual_mult": 0.8, "embedding": {"scale": 8.0}, "token_side": {"dim": 16},
-    "layers": [_moe(_parallel(4, 1, 64, 64, 0.125, 100, 5, 32, 4.0, 128, 16, 8, 4, 0.9, 0.7, 250000.0),
+    "layers": [_moe(_parallel(4, 1, 64, 64, 0.11, 100, 5, 32, 2.5, 128, 16, 8, 4, 0.9, 0.7, 300000.0),
                     8, 2, 3, 64, 1.5, (128, 1.0)),
-               _dense(_retention(2, 64, 128, [0.96875, 0.998], 64, 1000000.0), 384),
-               _dense(_parallel(8, 4, 64, 64, 0.11, 130, 0, 64, None, 96, 8, 4, 2, 1.0, 1.0), 192)],
+               _dense(_retention(2, 64, 128, [0.96875, 0.998], 64, 2000000.0), 384),
+               _dense(_parallel(8, 4, 64, 64, 0.14, 130, 0, 64, None, 96, 8, 4, 2, 1.0, 1.0), 192)],
 }
 # keys and values of 128 (the tensor-memory kernel's other size), kept tokens beyond the first
 # page, two retention layers in a row, a state of 64 per channel
