@@ -162,7 +162,7 @@ def selective_scan(x: torch.Tensor, w: Mapping[str, torch.Tensor], p: str, m: Ma
 def parallel(x: torch.Tensor, w: Mapping[str, torch.Tensor], p: str, m: Mapping, eps: float) -> torch.Tensor:
     left = windowed_attention(x, w, p + "left.", m["left"], eps)
     right = selective_scan(x, w, p + "right.", m["right"])
-    return m["left_scale"] * left + m["right_scale"] * right
+    return m.get("left_scale", 1.0) * left + m.get("right_scale", 1.0) * right
 
 
 # ---- feed-forwards -----------------------------------------------------------------------------

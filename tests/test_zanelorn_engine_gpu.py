@@ -65,7 +65,7 @@ def _plain(cfg, w, ids, dtype):
     return Plain(*P.forward_marked(cfg, w, ids, LEAST_MARGIN[dtype]))
 
 
-def _close(got, want, dtype):
+def _close(got, want, dtype, float32_bound=2e-5, few=0.1):
     """Row by row, in the order of the positions.  A router's close call may rightly go the other
     way in an engine that rounds otherwise; the token's logits then differ, and so do those of every
     later token (its keys, values and state go on in the mixers of later layers).  So: a row must be
@@ -81,11 +81,11 @@ def _close(got, want, dtype):
     w = want.logits
     top = max(1e-30, float(w.abs().max()))
     if dtype == "float32":
-        err, bound, worst, few = (g - w).abs().max(dim=-1).values / top, 2e-5, 2e-5, 0.0
+        err, bound, worst, few = (g - w).abs().max(dim=-1).values / top, float32_bound, float32_bound, 0.0
     else:
         from helpers import ROW_RMS_TOL
         err, bound = (g - w).pow(2).mean(dim=-1).sqrt() / top, ROW_RMS_TOL
-        worst, few = 16 * bound, 0.1
+        worst = 16 * bound
     checked, above = 0, 0
     for t in range(w.shape[0]):
         e = float(err[t])
