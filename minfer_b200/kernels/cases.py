@@ -533,6 +533,54 @@ def budanex_step_decode(reps, batch=8, ctx=2048):
     print(f"budanex decode step, batch {batch} at {ctx} positions, nine layer runs: {us:.1f} us")
 
 
+def _zanelorn_engine(max_tokens=8 * 4096, max_seqs=8):
+    from ..engine.step import Engine
+    from ..model import Model
+    moe = {"kind": "moe", "expert": {"ff": 2816, "limit": 7.0},
+           "router": {"experts": 8, "identity": 1, "top": 2}, "shared": {"ff": 2816, "limit": 7.0}}
+    dense = {"kind": "dense", "ff": 5632}
+    retention = {"type": "retention",
+                 "mixer": {"heads": 8, "dim": 128, "vdim": 256, "decay": [1.0 - 0.03 / (1 + i % 4) for i in range(8)],
+                           "rot": {"base": 500000.0, "dims": 64}}}
+    parallel = {"type": "parallel",
+                "mixer": {"left": {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                                   "mask": {"size": 1024, "keep_first": 4},
+                                   "rot": {"base": 100000.0, "dims": 64, "scaling": {"factor": 8.0}}},
+                          "right": {"inner": 2048, "state": 16, "dt_rank": 128, "conv": 4},
+                          "left_scale": 1.0, "right_scale": 0.75}}
+    layers = [dict(retention if i % 2 == 0 else parallel, mlp=moe if i % 3 == 0 else dense) for i in range(6)]
+    cfg = {"architecture": "Zanelorn", "vocab": 32000, "width": 2048, "norm": {"eps": 1e-6},
+           "residual_mult": 0.5, "embedding": {"scale": 12.0}, "token_side": {"dim": 64}, "layers": layers}
+    model = Model.from_config(cfg, seed=0, dtype="bfloat16", device="cuda:0", make_on="device")
+    return Engine(model, max_tokens=max_tokens, max_seqs=max_seqs, cuda_graphs=False), cfg
+
+
+def zanelorn_step_prefill(reps, tokens=2048):
+    """A whole prompt of 2,048 tokens through a Zanelorn model of width 2,048: six layers, retention
+    and attention beside a selective scan in turn, routed and dense feed-forwards, plus the head."""
+    eng, cfg = _zanelorn_engine()
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, cfg["vocab"], (tokens,), generator=g).tolist()
+
+    def run():
+        s = eng.acquire()
+        eng.step([s], [ids])
+        eng.release(s)
+    us = _time(run, reps, graph=False)
+    print(f"zanelorn prefill step, {tokens} tokens, six layers: {us:.1f} us")
+
+
+def zanelorn_step_decode(reps, batch=8, ctx=2048):
+    """Decode steps of 8 sequences at 2,048 positions through the same model, kernel by kernel."""
+    eng, cfg = _zanelorn_engine()
+    g = torch.Generator().manual_seed(0)
+    slots = [eng.acquire() for _ in range(batch)]
+    eng.step(slots, [torch.randint(0, cfg["vocab"], (ctx,), generator=g).tolist() for _ in range(batch)])
+    tokens = torch.randint(0, cfg["vocab"], (batch,), dtype=torch.int32, device="cuda")
+    us = _time(lambda: eng.decode_on_device(slots, tokens), reps, graph=False)
+    print(f"zanelorn decode step, batch {batch} at {ctx} positions, six layers: {us:.1f} us")
+
+
 CASES = {f.__name__: f for f in (gemm_decode, gemm_decode_split, gemm_decode_m64, gemm_decode_split_m64, gemm_prefill, gemm_prefill_down,
                                  gemm_decode_cluster, gemm_decode_cluster_o, gemm_decode_cluster_m64,
                                  attention_decode, attention_decode_b8, attention_decode_long, attention_prefill,
@@ -540,7 +588,8 @@ CASES = {f.__name__: f for f in (gemm_decode, gemm_decode_split, gemm_decode_m64
                                  attention_portion, attention_portion_512_on_8k,
                                  step_prefill, step_prefill_timeline, step_portions, step_decode, step_decode_sweep, step_prefill_sweep, step_decode_timeline,
                                  step_decode_timeline_b64, step_decode_b64, step_decode_small,
-                                 ssm_scan_prompt, ssm_scan_decode, budanex_step_prefill, budanex_step_decode)}
+                                 ssm_scan_prompt, ssm_scan_decode, budanex_step_prefill, budanex_step_decode,
+                                 zanelorn_step_prefill, zanelorn_step_decode)}
 
 
 def main(argv=None) -> int:

@@ -132,7 +132,6 @@ class TokenSide(Part):
                  eps: float, mult: float = 1.0, table_name: str = "side.embed",
                  gate_name: str = "side.gate", proj_name: str = "side.proj",
                  norm_name: str = "side.norm", init_std: float = 0.02):
-        from .linear import Linear  # noqa: F401  (the products below)
         if dim < 1 or offset < 0 or offset + dim > table_width:
             raise ValueError(f"columns [{offset}, {offset + dim}) do not lie within a table of {table_width}")
         self.hidden_size, self.vocab_size = int(hidden_size), int(vocab_size)
