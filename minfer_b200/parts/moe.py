@@ -96,6 +96,12 @@ class RoutedExperts(FeedForward):
         self.router_name, self.router_bias_name = router_name, router_bias_name
         self.expert_name = expert_name
         self.init_std, self.router_std = float(init_std), float(router_std)
+        # the per-token kernels keep a token's input and its experts' hidden values in shared memory;
+        # sizes beyond that always take the grouped path, which reads a few numbers back on the host
+        # and so cannot be part of a CUDA graph
+        self.per_token_fits = (4 * self.hidden_size <= 48 * 1024
+                               and 4 * self.top * self.intermediate_size <= 48 * 1024)
+        self.capturable = self.per_token_fits
         self.router: Optional[Linear] = None
         self.w_gate: Optional[torch.Tensor] = None       # [experts, ff, width]
         self.w_up: Optional[torch.Tensor] = None
@@ -213,7 +219,7 @@ class RoutedExperts(FeedForward):
             K.moe_route_scored(logits, self.correction, idx, wts, self.top, self.n_outputs)
         else:
             K.moe_route(logits, idx, wts, self.top)
-        if n <= PER_TOKEN_MAX or torch.cuda.is_current_stream_capturing():
+        if self.per_token_fits and (n <= PER_TOKEN_MAX or torch.cuda.is_current_stream_capturing()):
             hidden = torch.empty((n, self.top, self.intermediate_size), dtype=x.dtype, device=dev)
             K.moe_experts(x, self.w_gate, self.w_up, self.w_down, idx, wts, hidden, residual,
                           self.activation, self.limit, self.alpha)

@@ -432,6 +432,18 @@ def test_sizes_that_are_one(dtype):
     _run_cuts(cfg, 54, dtype, n=70)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_experts_wider_than_the_per_token_kernels_take(dtype):
+    """Four experts a token of 3,200 hidden values each do not fit the per-token kernels' shared
+    memory: every step, also of one token, groups the pairs by expert, and no step is captured."""
+    cfg = copy.deepcopy(ZAN_A)
+    cfg["layers"] = [cfg["layers"][1], cfg["layers"][0]]
+    cfg["layers"][0]["mlp"] = {"kind": "moe", "expert": {"ff": 3200, "limit": 1.0},
+                               "router": {"experts": 4, "identity": 1, "top": 4}, "shared": None}
+    eng = _run_cuts(cfg, 55, dtype)
+    assert not eng.cuda_graphs
+
+
 def test_matrices_stored_in_32_bit_run_in_the_bfloat16_engine():
     """A checkpoint whose matrices are float32 keeps them so in the bfloat16 engine (FP32-pipe
     products, bfloat16 cache and attention): every mixer and feed-forward takes the mix."""
