@@ -187,9 +187,9 @@ def route(x: torch.Tensor, w: Mapping[str, torch.Tensor], p: str, top: int):
     if ranked.shape[1] > top:
         # relative to the two scores it separates: rounding moves a score by a fraction of itself
         near = torch.gather(s, 1, order[:, top - 1:top + 1]).sum(dim=-1) / 2
+        # (small scores count too: the feed-forward's output is normed, and an expert without
+        # weights returns the token's whole input, so a weight of a thousandth can be most of it)
         margin = (ranked[:, top - 1] - ranked[:, top]) / near.clamp(min=1e-30)
-        # two experts whose scores are next to nothing may change places without a trace
-        margin = torch.where(near < 0.005, torch.full_like(margin, float("inf")), margin)
     else:
         margin = torch.full((x.shape[0],), float("inf"), dtype=x.dtype)
     return chosen, torch.gather(s, 1, chosen), margin
